@@ -1,6 +1,6 @@
 """One registry from an architecture's name to its configuration reader and its plan of parts.
 
-The name is ``architectures[0]`` of config.json (or ``model_type`` when that list is absent).  The
+The name is ``architectures[0]`` of config.json (or its ``architecture`` string, or ``model_type``).  The
 reference has a single decoder class and no registry (edgerag/core/loader.py:22-29); this is the
 seam through which another architecture is added without touching the engine.
 """
@@ -36,6 +36,8 @@ def architecture_names() -> list[str]:
 
 def architecture_of(raw: dict[str, Any], where: str = "config") -> Architecture:
     names = list(raw.get("architectures") or [])
+    if isinstance(raw.get("architecture"), str):
+        names.append(raw["architecture"])
     if raw.get("model_type"):
         names.append(raw["model_type"])
     for name in names:
@@ -64,6 +66,9 @@ def _register_builtin() -> None:
     register_architecture(
         ["LlamaForCausalLM", "SmolVLMForConditionalGeneration", "llama", "smolvlm"],
         DecoderConfig.from_dict, llama_plan)
+    from ..models.dokodra import DokodraConfig, dokodra_plan
+
+    register_architecture(["Dokodra", "dokodra"], DokodraConfig.from_dict, dokodra_plan)
 
 
 _register_builtin()

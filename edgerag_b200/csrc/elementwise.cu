@@ -10,14 +10,14 @@ using namespace erb;
 ERB_DEFINE_LAST_ERROR(erb_last_error)
 
 // ---------------------------------------------------------------------------------------------
-// Embedding: hidden[t, :] = table[ids[t], :]  or  embeds[embed_row[t], :]   (written as float)
+// Embedding: hidden[t, :] = scale * table[ids[t], :]  or  scale * embeds[embed_row[t], :]   (written as float)
 // An id outside [0, vocab) sets *status = 1 + t and writes zeros; nothing is read out of range.
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void embed_rows_kernel(float* __restrict__ hidden, const T* __restrict__ table,
                                   const T* __restrict__ embeds, const int* __restrict__ ids,
                                   const int* __restrict__ embed_row, int hidden_size, int vocab,
-                                  int n_embed_rows, int* __restrict__ status) {
+                                  int n_embed_rows, int* __restrict__ status, float scale) {
   chain_wait();
   const int t = blockIdx.x;
   const int er = embed_row ? embed_row[t] : -1;
@@ -30,17 +30,17 @@ __global__ void embed_rows_kernel(float* __restrict__ hidden, const T* __restric
   }
   if (!src && threadIdx.x == 0) atomicCAS(status, 0, 1 + t);
   float* dst = hidden + (size_t)t * hidden_size;
-  for (int i = threadIdx.x; i < hidden_size; i += blockDim.x) dst[i] = src ? Elem<T>::load(src + i) : 0.f;
+  for (int i = threadIdx.x; i < hidden_size; i += blockDim.x) dst[i] = src ? Elem<T>::load(src + i) * scale : 0.f;
 }
 
 ERB_EXPORT int erb_embed_rows(void* hidden, const void* table, const void* embeds, const int* ids,
                               const int* embed_row, int n_tokens, int hidden_size, int vocab,
-                              int n_embed_rows, int* status, void* stream) {
+                              int n_embed_rows, int* status, float scale, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   if (hidden_size <= 0 || vocab <= 0) return fail(ERB_ERR_ARG, "embed_rows: bad sizes");
   const int threads = hidden_size >= 1024 ? 256 : 128;
   launch_chained(embed_rows_kernel<elem_t>, dim3(n_tokens), dim3(threads), 0, (cudaStream_t)stream, (float*)hidden,
-      (const elem_t*)table, (const elem_t*)embeds, ids, embed_row, hidden_size, vocab, n_embed_rows, status);
+      (const elem_t*)table, (const elem_t*)embeds, ids, embed_row, hidden_size, vocab, n_embed_rows, status, scale);
   return check_launch("embed_rows");
 }
 
@@ -60,7 +60,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
                                    const float* __restrict__ parts, int n_parts, size_t part_stride,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ rows, int hidden_size, float eps,
-                                   int write_back) {
+                                   int write_back, int exact) {
   chain_wait();
   extern __shared__ float row_cache[];  // hidden_size floats, then 32 of scratch
   float* scratch = row_cache + hidden_size;
@@ -86,7 +86,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ hidden, const T* __restri
   const float rs = rsqrtf(total / (float)hidden_size + eps);
   T* y = out + (size_t)o * hidden_size;
   for (int i = threadIdx.x; i < hidden_size; i += blockDim.x) {
-    const float normed = Elem<T>::round(row_cache[i] * rs);
+    const float normed = exact ? row_cache[i] * rs : Elem<T>::round(row_cache[i] * rs);
     Elem<T>::store(y + i, weight[i] * normed);
   }
 }
@@ -126,8 +126,10 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
                                         const float* __restrict__ parts, int n_parts, size_t part_stride,
                                         const float* __restrict__ weight, T* __restrict__ out,
                                         const int* __restrict__ rows, int hidden_size, float eps,
-                                        int write_back, int settled) {
+                                        int write_back, int flags) {
   extern __shared__ float row_cache[];
+  const int settled = flags & 1;
+  const bool exact = flags & 2;        // the normed value is not rounded before the weight multiplies it
   float* scratch = REGS ? row_cache : row_cache + hidden_size;
   float keep[REGS ? R : 1][4];
   const int o = blockIdx.x;
@@ -222,7 +224,7 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
         load4(weight + i, w);
       }
 #pragma unroll
-      for (int j = 0; j < 4; ++j) v[j] = w[j] * Elem<T>::round(keep[q][j] * rs);
+      for (int j = 0; j < 4; ++j) v[j] = w[j] * (exact ? keep[q][j] * rs : Elem<T>::round(keep[q][j] * rs));
       Pack4<T>::store(y + i, v);
     }
     return;
@@ -237,7 +239,7 @@ add_rmsnorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta,
       load4(weight + i, w);
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) v[j] = w[j] * Elem<T>::round(v[j] * rs);
+    for (int j = 0; j < 4; ++j) v[j] = w[j] * (exact ? v[j] * rs : Elem<T>::round(v[j] * rs));
     Pack4<T>::store(y + i, v);
   }
 }
@@ -301,7 +303,7 @@ int run_add_rmsnorm(void* hidden, const void* delta, const float* parts, int n_p
           (const elem_t*)delta, nullptr, 0, (size_t)0, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled);
   } else {
     launch_chained(add_rmsnorm_kernel<elem_t>, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream, (float*)hidden,
-        (const elem_t*)delta, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps, write_back);
+        (const elem_t*)delta, parts, n_parts, part_stride, weight, (elem_t*)out, rows, hidden_size, eps, write_back, settled & 2);
   }
   return check_launch("add_rmsnorm");
 }
@@ -684,4 +686,54 @@ ERB_EXPORT int erb_resolve_ids(int* ids, int n, const int* fed, int n_fed, void*
   if (!ids || !fed || n_fed <= 0) return fail(ERB_ERR_ARG, "resolve_ids: no buffer of fed-back tokens");
   launch_chained(resolve_ids_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, (cudaStream_t)stream, ids, n, fed, n_fed);
   return check_launch("resolve_ids");
+}
+
+// ---------------------------------------------------------------------------------------------
+// A gated unit with bounded branches: with g = min(gate, limit) and u = clamp(up, -limit, limit),
+//   out[t, i] = g * sigmoid(alpha * g) * (u + shift),      gate = gate_up[t, i], up = gate_up[t, I + i],
+// computed in float.  limit <= 0 leaves both branches unbounded; (alpha, shift) = (1, 0) is SwiGLU.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void glu_bounded_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total,
+                                   float limit, float alpha, float shift) {
+  chain_wait();
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / inter;
+  const int i = (int)(idx % inter);
+  const T* row = gate_up + t * 2 * (size_t)inter;
+  float g = Elem<T>::load(row + i), u = Elem<T>::load(row + inter + i);
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  Elem<T>::store(out + idx, g / (1.f + expf(-alpha * g)) * (u + shift));
+}
+
+ERB_EXPORT int erb_glu_bounded(const void* gate_up, void* out, int n_tokens, int inter, float limit, float alpha,
+                               float shift, void* stream) {
+  if (n_tokens <= 0) return ERB_OK;
+  if (inter <= 0) return fail(ERB_ERR_ARG, "glu_bounded: bad intermediate size");
+  const size_t total = (size_t)n_tokens * inter;
+  launch_chained(glu_bounded_kernel<elem_t>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                 (const elem_t*)gate_up, (elem_t*)out, inter, total, limit, alpha, shift);
+  return check_launch("glu_bounded");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Soft cap of float logits in place: x <- cap * tanh(x / cap), rows `stride` floats apart.
+// ---------------------------------------------------------------------------------------------
+__global__ void softcap_kernel(float* __restrict__ x, int width, int stride, float cap) {
+  chain_wait();
+  float* row = x + (size_t)blockIdx.x * stride;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < width; i += gridDim.y * blockDim.x) row[i] = cap * tanhf(row[i] / cap);
+}
+
+ERB_EXPORT int erb_softcap(float* x, int n_rows, int width, int stride, float cap, void* stream) {
+  if (n_rows <= 0 || width <= 0) return ERB_OK;
+  if (!(cap > 0.f) || stride < width) return fail(ERB_ERR_ARG, "softcap: the cap must be positive and the stride cover a row");
+  int y = (width + 1023) / 1024;
+  if (y > 64) y = 64;
+  launch_chained(softcap_kernel, dim3(n_rows, y), dim3(256), 0, (cudaStream_t)stream, x, width, stride, cap);
+  return check_launch("softcap");
 }

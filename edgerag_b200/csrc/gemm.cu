@@ -212,6 +212,91 @@ ERB_EXPORT int erb_linear(const void* a, const void* w, void* out, int M, int N,
   return ERB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same product for `batch` independent triples that lie at fixed strides (in elements) from one
+// another:  out_b[M, N] = a_b[M, K] * w_b[N, K]^T.  The operands of a batch may interleave (a stride
+// smaller than a leading dimension): the heads of one activation row against a weight per head.
+// ---------------------------------------------------------------------------------------------
+namespace {
+using BatchKey = std::tuple<int, int, int, int, int, int, int, int, long long, long long, long long, size_t, int>;
+std::map<BatchKey, Plan> g_batch_plans;
+
+// Largest power of two (up to 256) that divides an address and the byte distances between its rows and batches.
+uint32_t alignment_of(const void* p, long long ld_bytes, long long stride_bytes) {
+  uintptr_t bits = (uintptr_t)p | (uintptr_t)ld_bytes | (uintptr_t)stride_bytes | 256u;
+  return (uint32_t)(bits & (~bits + 1));
+}
+}  // namespace
+
+ERB_EXPORT int erb_linear_batched(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw, int ldo,
+                                  int out_f32, int batch, long long stride_a, long long stride_w, long long stride_o,
+                                  void* workspace, long long ws_bytes, void* stream) {
+  if (M <= 0 || batch <= 0) return ERB_OK;
+  if (N <= 0 || K <= 0 || lda < K || ldw < K || ldo < N) return fail(ERB_ERR_ARG, "linear_batched: bad sizes");
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_handle) LT_CHECK(cublasLtCreate(&g_handle));
+  const size_t ws = workspace ? (size_t)ws_bytes : 0;
+#if ERB_ELEM == 0
+  const long long in_size = 4, out_size = 4;
+#else
+  const long long in_size = 2, out_size = out_f32 ? 4 : 2;
+#endif
+  // the library assumes 256-byte alignment unless told otherwise; interleaved batches start anywhere
+  const uint32_t align_a = alignment_of(a, lda * in_size, stride_a * in_size);
+  const uint32_t align_w = alignment_of(w, ldw * in_size, stride_w * in_size);
+  const uint32_t align_o = alignment_of(out, ldo * out_size, stride_o * out_size);
+  BatchKey key{M, N, K, lda, ldw, ldo, out_f32, batch, stride_a, stride_w, stride_o, ws,
+               (int)(align_a | (align_w << 10) | (align_o << 20))};
+  auto it = g_batch_plans.find(key);
+  if (it == g_batch_plans.end()) {
+    Plan p;
+#if ERB_ELEM == 0
+    const cudaDataType_t in_t = CUDA_R_32F, out_t = CUDA_R_32F;
+    if (!out_f32) return fail(ERB_ERR_ARG, "linear_batched: the float build writes float only");
+#else
+    const cudaDataType_t in_t = CUDA_R_16BF;
+    const cudaDataType_t out_t = out_f32 ? CUDA_R_32F : CUDA_R_16BF;
+#endif
+    LT_CHECK(cublasLtMatmulDescCreate(&p.op, CUBLAS_COMPUTE_32F, CUDA_R_32F));
+    const cublasOperation_t tt = CUBLAS_OP_T, nn = CUBLAS_OP_N;
+    LT_CHECK(cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSA, &tt, sizeof(tt)));
+    LT_CHECK(cublasLtMatmulDescSetAttribute(p.op, CUBLASLT_MATMUL_DESC_TRANSB, &nn, sizeof(nn)));
+    LT_CHECK(cublasLtMatrixLayoutCreate(&p.a, in_t, K, N, ldw));
+    LT_CHECK(cublasLtMatrixLayoutCreate(&p.b, in_t, K, M, lda));
+    LT_CHECK(cublasLtMatrixLayoutCreate(&p.c, out_t, N, M, ldo));
+    const int32_t count = batch;
+    const int64_t sw = stride_w, sa = stride_a, so = stride_o;
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(p.a, CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &count, sizeof(count)));
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(p.a, CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &sw, sizeof(sw)));
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(p.b, CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &count, sizeof(count)));
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(p.b, CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &sa, sizeof(sa)));
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(p.c, CUBLASLT_MATRIX_LAYOUT_BATCH_COUNT, &count, sizeof(count)));
+    LT_CHECK(cublasLtMatrixLayoutSetAttribute(p.c, CUBLASLT_MATRIX_LAYOUT_STRIDED_BATCH_OFFSET, &so, sizeof(so)));
+    cublasLtMatmulPreference_t pref;
+    LT_CHECK(cublasLtMatmulPreferenceCreate(&pref));
+    LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &ws, sizeof(ws)));
+    LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_A_BYTES, &align_w, sizeof(align_w)));
+    LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_B_BYTES, &align_a, sizeof(align_a)));
+    LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_C_BYTES, &align_o, sizeof(align_o)));
+    LT_CHECK(cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MIN_ALIGNMENT_D_BYTES, &align_o, sizeof(align_o)));
+    int found = 0;
+    cublasStatus_t st = cublasLtMatmulAlgoGetHeuristic(g_handle, p.op, p.a, p.b, p.c, p.c, pref, 1, p.candidates, &found);
+    cublasLtMatmulPreferenceDestroy(pref);
+    if (st != CUBLAS_STATUS_SUCCESS || found == 0)
+      return fail(ERB_ERR_UNSUPPORTED, "linear_batched: no cuBLASLt algorithm for %d x (M=%d N=%d K=%d lda=%d ldw=%d ldo=%d) (%s)",
+                  batch, M, N, K, lda, ldw, ldo, status_name(st));
+    p.n_candidates = found;
+    p.algo = p.candidates[0].algo;
+    p.tuned = true;
+    it = g_batch_plans.emplace(key, p).first;
+  }
+  Plan& p = it->second;
+  const float alpha = 1.f, beta = 0.f;
+  LT_CHECK(cublasLtMatmul(g_handle, p.op, &alpha, w, p.a, a, p.b, &beta, out, p.c, out, p.c, &p.algo, workspace, ws,
+                          (cudaStream_t)stream));
+  return ERB_OK;
+}
+
 #if ERB_ELEM == 1
 // ---------------------------------------------------------------------------------------------
 // Weight-streaming product for few rows (decode): out[M, N] = a[M, K] * w[N, K]^T, M <= 64,

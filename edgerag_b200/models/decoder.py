@@ -27,8 +27,10 @@ class DecoderModel:
         for layer in plan.layers:
             norm1 = build_part("norm", layer.norm1, dtype, device)
             mixer = build_part("mixer", layer.mixer, dtype, device)
-            norm2 = build_part("norm", layer.norm2, dtype, device)
-            ffn = build_part("ffn", layer.ffn, dtype, device)
+            if (layer.norm2 is None) != (layer.ffn is None):
+                raise ValueError(f"layer {layer.prefix!r}: a second norm and a feed-forward come together or not at all")
+            norm2 = build_part("norm", layer.norm2, dtype, device) if layer.norm2 is not None else None
+            ffn = build_part("ffn", layer.ffn, dtype, device) if layer.ffn is not None else None
             try:
                 block_cls = _REGISTRY["block"][layer.block.kind]
             except KeyError:
@@ -38,7 +40,8 @@ class DecoderModel:
             self.blocks.append(block)
             for spec, part in ((layer.norm1, norm1), (layer.mixer, mixer), (layer.norm2, norm2),
                                (layer.ffn, ffn), (layer.block, block)):
-                self._owners.append((layer.prefix + spec.prefix, part))
+                if part is not None:
+                    self._owners.append((layer.prefix + spec.prefix, part))
         self.final_norm = build_part("norm", plan.final_norm, dtype, device) if plan.final_norm else None
         if self.final_norm is not None:
             self._owners.append((plan.final_norm.prefix, self.final_norm))

@@ -24,7 +24,7 @@ _ELEM = {torch.float32: "float32", torch.bfloat16: "bfloat16"}
 
 _SIGNATURES = {
     "erb_embed_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                       c_void_p, c_void_p],
+                       c_void_p, c_float, c_void_p],
     "erb_add_rmsnorm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int,
                         c_void_p],
     "erb_residual_add": [c_void_p, c_void_p, c_longlong, c_void_p],
@@ -64,6 +64,24 @@ _SIGNATURES = {
     "erb_attention_decode_gqa": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_void_p, c_void_p, c_void_p],
+    "erb_glu_bounded": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p],
+    "erb_softcap": [c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "erb_linear_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p],
+    "erb_latent_store": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int,
+                         c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+    "erb_latent_q_rotate": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                            c_void_p],
+    "erb_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                             c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                             c_void_p],
+    "erb_conv_silu": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_void_p],
+    "erb_conv_state_update": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "erb_ssm_scan": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_gated_group_norm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                             c_float, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
 }
 
@@ -71,7 +89,7 @@ _functions: dict[tuple[str, str | None, str], object] = {}
 
 #: launches issued through this module: this package's own kernels, and library products
 launch_counts = {"own": 0, "library": 0}
-_LAUNCHES = {"erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
+_LAUNCHES = {"erb_linear_batched": 0, "erb_attention_decode": 2, "erb_attention_prefill_tc": 1, "erb_attention_decode_bulk": 1, "erb_attention_decode_gqa": 1, "erb_linear": 0}
 SKINNY_MAX_ROWS = 16     # rows up to which the register-fed weight-streaming kernels are used
 TC_MAX_ROWS = 64         # rows up to which the TMA + tcgen05 weight-streaming kernel may be used
 
@@ -136,8 +154,8 @@ def _need(t: torch.Tensor | None, name: str, dtype=None, contiguous: bool = True
 # --- rows ------------------------------------------------------------------------------------
 
 def embed_rows(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, status: torch.Tensor,
-               embeds: torch.Tensor | None = None, embed_row: torch.Tensor | None = None) -> None:
-    """hidden[t] = table[ids[t]], or embeds[embed_row[t]] where embed_row[t] >= 0 (float output)."""
+               embeds: torch.Tensor | None = None, embed_row: torch.Tensor | None = None, scale: float = 1.0) -> None:
+    """hidden[t] = scale * table[ids[t]], or scale * embeds[embed_row[t]] where embed_row[t] >= 0 (float output)."""
     n, h = hidden.shape
     _need(hidden, "hidden", torch.float32); _need(table, "table"); _need(ids, "ids", torch.int32)
     _need(status, "status", torch.int32); _need(embed_row, "embed_row", torch.int32)
@@ -149,13 +167,14 @@ def embed_rows(hidden: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, sta
             raise KernelError("embed_rows: embeds need embed_row and the hidden width")
     _call(_fn("elementwise", _elem(table), "erb_embed_rows"), hidden.data_ptr(), table.data_ptr(),
           _ptr(embeds), ids.data_ptr(), _ptr(embed_row), n, h, table.shape[0],
-          0 if embeds is None else embeds.shape[0], status.data_ptr(), _stream())
+          0 if embeds is None else embeds.shape[0], status.data_ptr(), float(scale), _stream())
 
 
 def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
                 delta: torch.Tensor | None = None, rows: torch.Tensor | None = None,
-                write_back: bool = True, settled: bool = False) -> None:
+                write_back: bool = True, settled: bool = False, exact: bool = False) -> None:
     """out = weight * round(rmsnorm(hidden (+ delta))); hidden += delta in place when write_back.
+    ``exact``: the normed value stays float until the weight has multiplied it (one rounding, at the store).
     ``delta``: rows of the element type, or float32 partial sums ``[parts, rows, width]`` (what
     ``linear_parts`` leaves) that are added in their order and rounded to the element type once, so that
     the update is what a product stored in the element type would have been.
@@ -176,10 +195,11 @@ def add_rmsnorm(hidden: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, e
     if in_parts:
         _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm_parts"), hidden.data_ptr(), delta.data_ptr(), delta.shape[0],
               delta.stride(0), weight.data_ptr(), out.data_ptr(), _ptr(rows), n, h, float(eps),
-              int(write_back and rows is None), int(bool(settled)), _stream())
+              int(write_back and rows is None), int(bool(settled)) | (2 if exact else 0), _stream())
         return
     _call(_fn("elementwise", _elem(out), "erb_add_rmsnorm"), hidden.data_ptr(), _ptr(delta), weight.data_ptr(),
-          out.data_ptr(), _ptr(rows), n, h, float(eps), int(write_back and rows is None), int(bool(settled)), _stream())
+          out.data_ptr(), _ptr(rows), n, h, float(eps), int(write_back and rows is None),
+          int(bool(settled)) | (2 if exact else 0), _stream())
 
 
 def residual_add(hidden: torch.Tensor, delta: torch.Tensor, dtype: torch.dtype | None = None) -> None:
@@ -248,6 +268,28 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     if gate_up.shape != (n, 2 * inter):
         raise KernelError("swiglu: gate_up must be [tokens, 2 * intermediate]")
     _call(_fn("elementwise", _elem(out), "erb_swiglu"), gate_up.data_ptr(), out.data_ptr(), n, inter, _stream())
+
+
+def glu_bounded(gate_up: torch.Tensor, out: torch.Tensor, limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0) -> None:
+    """out[t, i] = g * sigmoid(alpha * g) * (u + shift) with g = min(gate_up[t, i], limit) and
+    u = clamp(gate_up[t, I + i], -limit, limit); ``limit <= 0`` bounds nothing."""
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    n, inter = out.shape
+    if gate_up.shape != (n, 2 * inter):
+        raise KernelError("glu_bounded: gate_up must be [tokens, 2 * intermediate]")
+    _call(_fn("elementwise", _elem(out), "erb_glu_bounded"), gate_up.data_ptr(), out.data_ptr(), n, inter, float(limit),
+          float(alpha), float(shift), _stream())
+
+
+def softcap(logits: torch.Tensor, cap: float, dtype: torch.dtype) -> None:
+    """logits <- cap * tanh(logits / cap) in place (float rows with unit inner stride).  ``dtype`` only
+    picks the library that holds the kernel (the engine's element type)."""
+    _need(logits, "logits", torch.float32, contiguous=False)
+    if logits.dim() != 2 or logits.stride(1) != 1:
+        raise KernelError("softcap: logits must be rows with unit inner stride")
+    n, width = logits.shape
+    _call(_fn("elementwise", _ELEM[dtype], "erb_softcap"), logits.data_ptr(), n, width, logits.stride(0) if n > 1 else width,
+          float(cap), _stream())
 
 
 # --- matrix products -------------------------------------------------------------------------
@@ -526,6 +568,182 @@ def linear(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, accumulate:
     ws = _workspace(a.device)
     _call(_fn("gemm", _elem(a), "erb_linear"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
           lda, k, ldo, int(out.dtype == torch.float32), int(accumulate), ws.data_ptr(), ws.numel(), _stream())
+
+
+def linear_batched(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[:, b, :] = a[:, b, :] @ weight[b]^T for every b: ``a`` ``[M, B, K]``, ``weight`` ``[B, N, K]``
+    contiguous, ``out`` ``[M, B, N]`` (float32 or the input type); ``a`` and ``out`` may be views with
+    any row and batch strides (unit inner stride): the heads of a row against a matrix per head.
+    One library call (float accumulation, no TF32)."""
+    _need(a, "a", contiguous=False); _need(weight, "weight", a.dtype); _need(out, "out", contiguous=False)
+    m, b, k = a.shape
+    n = weight.shape[1]
+    if weight.shape != (b, n, k) or out.shape != (m, b, n) or a.stride(2) != 1 or out.stride(2) != 1:
+        raise KernelError("linear_batched: shapes or strides disagree")
+    if out.dtype not in (a.dtype, torch.float32):
+        raise KernelError("linear_batched: out must be float32 or the input type")
+    if m == 0:
+        return
+    lda = a.stride(0) if m > 1 else max(k, a.stride(0))
+    ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
+    ws = _workspace(a.device)
+    _call(_fn("gemm", _elem(a), "erb_linear_batched"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, lda, k, ldo,
+          int(out.dtype == torch.float32), b, a.stride(1), n * k, out.stride(1), ws.data_ptr(), ws.numel(), _stream())
+
+
+# --- attention through a latent ----------------------------------------------------------------
+
+def latent_store(proj: torch.Tensor, positions: torch.Tensor, eps: float, *, off_kv: int = -1, rank: int = 0, rot_dim: int = 0,
+                 kv_weight: torch.Tensor | None = None, inv_freq: torch.Tensor | None = None, rot_dims: int = 0,
+                 slots: torch.Tensor | None = None, pages: torch.Tensor | None = None, off_q: int = 0, q_rank: int = 0,
+                 q_weight: torch.Tensor | None = None, q_latent: torch.Tensor | None = None) -> None:
+    """From each token's row of a fused projection: (``off_kv >= 0``) the cache row ``[unit_rms(row[off_kv :
+    off_kv + rank]) * kv_weight | pairs of the next rot_dim entries turned by the position]`` written to slot
+    ``slots[t]`` of ``pages`` (``[n_pages, 1, page_size, rank + rot_dim]``); (``q_rank > 0``) ``q_latent[t] =
+    unit_rms(row[off_q : off_q + q_rank]) * q_weight``."""
+    _need(proj, "proj", contiguous=False); _need(positions, "positions", torch.int32)
+    _need(kv_weight, "kv_weight", torch.float32); _need(q_weight, "q_weight", torch.float32)
+    _need(inv_freq, "inv_freq", torch.float32); _need(slots, "slots", torch.int32)
+    _need(pages, "pages", proj.dtype); _need(q_latent, "q_latent", proj.dtype)
+    n = proj.shape[0]
+    if proj.stride(1) != 1 or positions.numel() < n:
+        raise KernelError("latent_store: proj must be rows with unit inner stride, one position per row")
+    if off_kv >= 0:
+        if pages is None or slots is None or kv_weight is None or pages.shape[-1] != rank + rot_dim or pages.shape[1] != 1:
+            raise KernelError("latent_store: pages must be [pages, 1, page_size, rank + rot_dim]")
+        if off_kv + rank + rot_dim > proj.shape[1] or kv_weight.numel() != rank or slots.numel() < n:
+            raise KernelError("latent_store: the down-projection lies outside the row")
+        if rot_dims and (inv_freq is None or inv_freq.numel() != rot_dims // 2):
+            raise KernelError("latent_store: inv_freq must hold rot_dims / 2 values")
+    if q_rank and (q_weight is None or q_latent is None or q_weight.numel() != q_rank or off_q + q_rank > proj.shape[1]
+                   or q_latent.shape != (n, q_rank)):
+        raise KernelError("latent_store: the query latent lies outside the row or its target has another shape")
+    _call(_fn("latent_attention", _elem(proj), "erb_latent_store"), proj.data_ptr(), n, proj.stride(0) if n > 1 else proj.shape[1],
+          int(off_kv), int(rank), int(rot_dim), _ptr(kv_weight), float(eps), positions.data_ptr(), _ptr(inv_freq), int(rot_dims),
+          _ptr(slots), _ptr(pages), int(off_q), int(q_rank), _ptr(q_weight), _ptr(q_latent), _stream())
+
+
+def latent_q_rotate(q: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor | None, n_heads: int, dim: int,
+                    rot_dim: int, rank: int, rot_dims: int, q_lat: torch.Tensor) -> None:
+    """q rows hold per head ``dim`` plain then ``rot_dim`` rotated entries; the latter go, pairs turned by
+    the position, to ``q_lat[t, head, rank:]`` (float ``[tokens, heads, rank + rot_dim]``)."""
+    _need(q, "q", contiguous=False); _need(positions, "positions", torch.int32); _need(inv_freq, "inv_freq", torch.float32)
+    _need(q_lat, "q_lat", torch.float32)
+    n = q.shape[0]
+    if q.stride(1) != 1 or q.shape[1] < n_heads * (dim + rot_dim) or q_lat.shape != (n, n_heads, rank + rot_dim):
+        raise KernelError("latent_q_rotate: shapes disagree")
+    _call(_fn("latent_attention", _elem(q), "erb_latent_q_rotate"), q.data_ptr(), n, q.stride(0) if n > 1 else q.shape[1],
+          n_heads, dim, rot_dim, rank, positions.data_ptr(), _ptr(inv_freq), int(rot_dims), q_lat.data_ptr(), _stream())
+
+
+def latent_scratch_floats(n_tokens: int, n_heads: int, rank: int, n_splits: int) -> int:
+    return n_tokens * n_heads * n_splits * (rank + 2) if n_splits > 1 else 0
+
+
+def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, seq_of_token: torch.Tensor,
+                     positions: torch.Tensor, out: torch.Tensor, scale: float, first_token: int, n_tokens: int, *,
+                     gate: torch.Tensor | None = None, sink: torch.Tensor | None = None, split_keys: int = 0,
+                     n_splits: int = 1, part: torch.Tensor | None = None) -> None:
+    """Causal multi-query attention of tokens ``first_token .. first_token + n_tokens`` over their sequences'
+    cache rows ``[c | kr]``: ``q_lat`` float ``[tokens, heads, rank + rot]`` (absorbed and rotated queries),
+    ``out[t, h] = gate(t, h) * softmax_j(scale * q_lat[t, h] . row_j (+ sink_h in the denominator)) @ c_j``
+    as ``[tokens, heads, rank]``.  ``gate``: ``[tokens, heads]`` logits (a view with unit inner stride) whose
+    sigmoid multiplies the result.  With ``n_splits > 1`` the keys are cut at multiples of ``split_keys`` and
+    ``part`` takes the splits' states."""
+    _need(q_lat, "q_lat", torch.float32); _need(pages, "pages"); _need(block_tables, "block_tables", torch.int32)
+    _need(seq_of_token, "seq_of_token", torch.int32); _need(positions, "positions", torch.int32)
+    _need(out, "out", pages.dtype); _need(gate, "gate", pages.dtype, contiguous=False); _need(sink, "sink", torch.float32)
+    _need(part, "part", torch.float32)
+    n, heads, dk = q_lat.shape
+    rank = out.shape[2]
+    page_size = pages.shape[2]
+    if pages.shape[1] != 1 or pages.shape[3] != dk or out.shape[:2] != (n, heads) or rank > dk:
+        raise KernelError("latent_attention: q_lat, pages and out disagree")
+    if first_token < 0 or first_token + n_tokens > n or seq_of_token.numel() < n or positions.numel() < n:
+        raise KernelError("latent_attention: the token range lies outside the batch")
+    if gate is not None and (gate.shape != (n, heads) or gate.stride(1) != 1):
+        raise KernelError("latent_attention: gate must be [tokens, heads] with unit inner stride")
+    if sink is not None and sink.numel() != heads:
+        raise KernelError("latent_attention: one sink per head")
+    if n_splits > 1 and (part is None or part.numel() < latent_scratch_floats(n_tokens, heads, rank, n_splits)):
+        raise KernelError("latent_attention: the scratch for the splits is too small")
+    fn = _fn("latent_attention", _elem(pages), "erb_latent_attention")
+    fn._erb_own = 2 if n_splits > 1 else 1
+    _call(fn, q_lat.data_ptr(), pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_of_token.data_ptr(),
+          positions.data_ptr(), _ptr(gate), 0 if gate is None else (gate.stride(0) if n > 1 else heads), _ptr(sink),
+          out.data_ptr(), _ptr(part), int(first_token), int(n_tokens), heads, rank, dk - rank, page_size, int(split_keys),
+          int(n_splits), float(scale), _stream())
+
+
+# --- state-space mixer -------------------------------------------------------------------------
+
+def conv_silu(proj: torch.Tensor, off: int, weight: torch.Tensor, bias: torch.Tensor | None, conv_state: torch.Tensor,
+              seq_of_token: torch.Tensor, seq_starts: torch.Tensor, state_slots: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, ch] = silu(bias[ch] + sum_j weight[ch, j] * input(t - (taps - 1 - j), ch)) over columns ``off ..
+    off + channels`` of ``proj``; inputs before the portion's first token come from the request's record in
+    ``conv_state`` (float ``[slots, taps - 1, channels]``, oldest first; zeros for a new request)."""
+    _need(proj, "proj", contiguous=False); _need(weight, "weight", proj.dtype); _need(bias, "bias", proj.dtype)
+    _need(conv_state, "conv_state", torch.float32); _need(out, "out", proj.dtype)
+    for name, t in (("seq_of_token", seq_of_token), ("seq_starts", seq_starts), ("state_slots", state_slots)):
+        _need(t, name, torch.int32)
+    n = proj.shape[0]
+    channels, taps = weight.shape
+    if proj.stride(1) != 1 or off + channels > proj.shape[1] or out.shape != (n, channels) or \
+            tuple(conv_state.shape[1:]) != (taps - 1, channels):
+        raise KernelError("conv_silu: shapes disagree")
+    _call(_fn("ssm", _elem(proj), "erb_conv_silu"), proj.data_ptr(), n, proj.stride(0) if n > 1 else proj.shape[1], int(off),
+          channels, taps, weight.data_ptr(), _ptr(bias), conv_state.data_ptr(), seq_of_token.data_ptr(), seq_starts.data_ptr(),
+          state_slots.data_ptr(), out.data_ptr(), _stream())
+
+
+def conv_state_update(proj: torch.Tensor, off: int, conv_state: torch.Tensor, n_seqs: int, seq_starts: torch.Tensor,
+                      state_slots: torch.Tensor) -> None:
+    """Every request's record in ``conv_state`` becomes the last ``taps - 1`` inputs of (record, then the step's rows)."""
+    _need(proj, "proj", contiguous=False); _need(conv_state, "conv_state", torch.float32)
+    _need(seq_starts, "seq_starts", torch.int32); _need(state_slots, "state_slots", torch.int32)
+    n = proj.shape[0]
+    _, keep, channels = conv_state.shape
+    if off + channels > proj.shape[1] or seq_starts.numel() < n_seqs + 1 or state_slots.numel() < n_seqs:
+        raise KernelError("conv_state_update: shapes disagree")
+    _call(_fn("ssm", _elem(proj), "erb_conv_state_update"), proj.data_ptr(), int(n_seqs), proj.stride(0) if n > 1 else proj.shape[1],
+          int(off), channels, keep + 1, conv_state.data_ptr(), seq_starts.data_ptr(), state_slots.data_ptr(), _stream())
+
+
+def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, off_dt: int, dt_bias: torch.Tensor, a_log: torch.Tensor, d_skip: torch.Tensor,
+             state: torch.Tensor, n_seqs: int, seq_starts: torch.Tensor, state_slots: torch.Tensor, y: torch.Tensor,
+             n_groups: int) -> None:
+    """The recurrence of the state-space mixer over every request's rows, from and to its record in ``state``
+    (float ``[slots, heads, N, P]``): ``xbc`` rows ``[x (heads * P) | B (groups * N) | C (groups * N)]``, raw
+    step sizes in columns ``off_dt .. off_dt + heads`` of ``proj``; ``y`` float ``[tokens, heads * P]``."""
+    _need(xbc, "xbc"); _need(proj, "proj", xbc.dtype, contiguous=False); _need(state, "state", torch.float32)
+    _need(y, "y", torch.float32)
+    for name, t in (("dt_bias", dt_bias), ("a_log", a_log), ("d_skip", d_skip)):
+        _need(t, name, torch.float32)
+    _need(seq_starts, "seq_starts", torch.int32); _need(state_slots, "state_slots", torch.int32)
+    n = xbc.shape[0]
+    _, heads, n_state, p = state.shape
+    if xbc.shape[1] != heads * p + 2 * n_groups * n_state or y.shape != (n, heads * p) or off_dt + heads > proj.shape[1] or \
+            dt_bias.numel() != heads or a_log.numel() != heads or d_skip.numel() != heads or proj.shape[0] != n:
+        raise KernelError("ssm_scan: shapes disagree")
+    _call(_fn("ssm", _elem(xbc), "erb_ssm_scan"), xbc.data_ptr(), xbc.shape[1], proj.data_ptr(),
+          proj.stride(0) if n > 1 else proj.shape[1], int(off_dt), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(),
+          state.data_ptr(), seq_starts.data_ptr(), state_slots.data_ptr(), y.data_ptr(), int(n_seqs), heads, p, n_state,
+          int(n_groups), _stream())
+
+
+def gated_group_norm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float, parts: int = 1,
+                     gate: torch.Tensor | None = None) -> None:
+    """out = unit_rms(x * silu(gate)) * weight, the mean square taken over each of ``parts`` equal pieces of a
+    row; ``x`` float32 or the element type, ``gate`` (optional) and ``out`` the element type; row-strided views allowed."""
+    _need(x, "x", contiguous=False); _need(weight, "weight", torch.float32); _need(out, "out", contiguous=False)
+    _need(gate, "gate", out.dtype, contiguous=False)
+    n, width = out.shape
+    if x.shape != (n, width) or weight.numel() != width or x.dtype not in (torch.float32, out.dtype) or \
+            x.stride(1) != 1 or out.stride(1) != 1 or (gate is not None and (gate.shape != (n, width) or gate.stride(1) != 1)):
+        raise KernelError("gated_group_norm: shapes or types disagree")
+    ld = lambda t: t.stride(0) if n > 1 else width   # noqa: E731
+    _call(_fn("ssm", _elem(out), "erb_gated_group_norm"), x.data_ptr(), int(x.dtype == torch.float32), ld(x), _ptr(gate), 0 if gate is None else ld(gate), weight.data_ptr(), out.data_ptr(), ld(out), n, width, int(parts),
+          float(eps), _stream())
 
 
 # --- attention -------------------------------------------------------------------------------

@@ -31,6 +31,8 @@ PACKAGE_EXT = Path(__file__).resolve().parent.parent / "_ext"
 LIBRARIES: dict[str, tuple[str, tuple[str, ...], bool]] = {
     "elementwise": ("elementwise.cu", (), True),
     "attention": ("attention.cu", (), True),
+    "latent_attention": ("latent_attention.cu", (), True),
+    "ssm": ("ssm.cu", (), True),
     "attention_tc": ("attention_tc.cu", ("-lcuda",), False),
     "attention_prefill": ("attention_prefill.cu", ("-lcuda",), False),
     "gemm": ("gemm.cu", ("-lcublasLt",), True),

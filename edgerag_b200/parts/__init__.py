@@ -2,7 +2,7 @@
 
 from .base import (Block, FeedForward, LayerCall, LayerSpec, Mixer, ModelPlan, Norm, Part, PartSpec,
                    PositionEncoding, WeightSpec, build_part, register_part, registered)
-from . import attention, block, embedding, rmsnorm, rope, swiglu  # noqa: F401  (registration)
+from . import attention, block, embedding, glu, latent_attention, rmsnorm, rope, ssd, swiglu  # noqa: F401  (registration)
 
 __all__ = ["Block", "FeedForward", "LayerCall", "LayerSpec", "Mixer", "ModelPlan", "Norm", "Part", "PartSpec",
            "PositionEncoding", "WeightSpec", "build_part", "register_part", "registered"]

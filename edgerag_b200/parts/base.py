@@ -64,8 +64,9 @@ class LayerSpec:
     block: PartSpec
     norm1: PartSpec
     mixer: PartSpec
-    norm2: PartSpec
-    ffn: PartSpec
+    #: None (both): the layer ends after its mixer's sublayer
+    norm2: PartSpec | None
+    ffn: PartSpec | None
 
 
 @dataclass(frozen=True)

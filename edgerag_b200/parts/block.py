@@ -18,8 +18,9 @@ from .base import Block, FeedForward, LayerCall, Mixer, Norm, register_part
 class PreNormBlock(Block):
     graph_safe = True
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward, hidden: int,
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm | None, ffn: FeedForward | None, hidden: int,
                  dtype: torch.dtype, device: torch.device) -> None:
+        """``norm2`` and ``ffn`` are None for a layer that is its mixer's sublayer only."""
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
         self.hidden = hidden
         self.dtype = dtype
@@ -35,6 +36,8 @@ class PreNormBlock(Block):
         if delta is not None:
             ctx.stream_written = kernels.launches()
         mixed = self.mixer.forward(x, ctx, call)
+        if self.ffn is None:
+            return mixed                               # added by whichever norm comes next
         self.norm2.forward(hidden, x, mixed, settled=settled())   # hidden += mixed; x = norm2(hidden)
         ctx.stream_written = kernels.launches()
         return self.ffn.forward(x, ctx)               # added by whichever norm comes next

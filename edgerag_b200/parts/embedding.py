@@ -1,6 +1,6 @@
 """Input and output ends of the decoder.
 
-``TokenEmbedding``: a plain table lookup without scale, or rows of caller-given embeddings
+``TokenEmbedding``: a table lookup (times a constant where the model has one), or rows of caller-given embeddings
 (edgerag/core/model.py:106-110: exactly one of ids and embeddings per token); the result is
 written to the float32 residual stream.  ``LMHead``: bias-free projection to float32 logits over
 the rows that were asked for (edgerag/core/model.py:150-152); where the plan names a tensor to
@@ -19,20 +19,23 @@ from .base import Part, WeightSpec, register_part
 class TokenEmbedding(Part):
     graph_safe = True
 
-    def __init__(self, vocab: int, hidden: int, dtype: torch.dtype, device: torch.device) -> None:
+    def __init__(self, vocab: int, hidden: int, dtype: torch.dtype, device: torch.device, scale: float = 1.0,
+                 tensor: str = "weight") -> None:
+        """``scale`` multiplies every row as it enters the float32 stream; ``tensor`` names the table."""
         self.vocab, self.hidden = vocab, hidden
         self.dtype, self.device = dtype, device
+        self.scale, self.tensor = float(scale), tensor
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec("weight", (self.vocab, self.hidden))]
+        return [WeightSpec(self.tensor, (self.vocab, self.hidden))]
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].to(device=self.device, dtype=self.dtype).contiguous()
+        self.weight = tensors[self.tensor].to(device=self.device, dtype=self.dtype).contiguous()
 
     def forward(self, ctx, hidden: torch.Tensor) -> None:
         kernels.embed_rows(hidden, self.weight, ctx.token_ids, ctx.status, embeds=ctx.embeds,
-                           embed_row=ctx.embed_row if ctx.embeds is not None else None)
+                           embed_row=ctx.embed_row if ctx.embeds is not None else None, scale=self.scale)
 
 
 @register_part("head", "linear")
@@ -40,18 +43,22 @@ class LMHead(Part):
     graph_safe = True
 
     def __init__(self, vocab: int, hidden: int, dtype: torch.dtype, device: torch.device,
-                 tied_to: str | None = None) -> None:
+                 tied_to: str | None = None, softcap: float = 0.0, tensor: str = "weight") -> None:
         """``tied_to``: model-relative name of the tensor to share when the checkpoint has no head of
-        its own (the plan names it; this part does not know what the model calls its embedding)."""
+        its own (the plan names it; this part does not know what the model calls its embedding).
+        ``softcap`` c > 0: logits <- c * tanh(logits / c), in float."""
         self.vocab, self.hidden, self.tied_to = vocab, hidden, tied_to
         self.dtype, self.device = dtype, device
+        self.softcap, self.tensor = float(softcap or 0.0), tensor
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec("weight", (self.vocab, self.hidden), fallback=self.tied_to)]
+        return [WeightSpec(self.tensor, (self.vocab, self.hidden), fallback=self.tied_to)]
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].to(device=self.device, dtype=self.dtype).contiguous()
+        self.weight = tensors[self.tensor].to(device=self.device, dtype=self.dtype).contiguous()
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor) -> None:
         kernels.linear(x, self.weight, logits)
+        if self.softcap > 0.0:
+            kernels.softcap(logits, self.softcap, self.dtype)

@@ -18,18 +18,27 @@ from .base import Norm, WeightSpec, register_part
 class RMSNorm(Norm):
     graph_safe = True
 
-    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device) -> None:
+    def __init__(self, size: int, eps: float, dtype: torch.dtype, device: torch.device, weight_offset: float = 0.0,
+                 exact: bool = False, tensor: str = "weight") -> None:
+        """``weight_offset``: the stored tensor is the scale minus this (1.0 for weights kept around zero);
+        ``exact``: the normed value is not rounded to the element type before the scale multiplies it, so the
+        norm is float up to its store; ``tensor``: the tensor's name below the part's prefix."""
         self.size = size
         self.eps = float(eps)
         self.dtype = dtype
         self.device = device
+        self.weight_offset = float(weight_offset)
+        self.exact = bool(exact)
+        self.tensor = tensor
         self.weight: torch.Tensor | None = None
 
     def weight_specs(self) -> list[WeightSpec]:
-        return [WeightSpec("weight", (self.size,), kind="vector32")]
+        return [WeightSpec(self.tensor, (self.size,), kind="vector32")]
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].to(device=self.device, dtype=torch.float32).contiguous()
+        w = tensors[self.tensor].to(device=self.device, dtype=torch.float32)
+        self.weight = (w + self.weight_offset if self.weight_offset else w).contiguous()
 
     def forward(self, hidden, out, delta=None, rows=None, write_back=True, settled=False) -> None:
-        kernels.add_rmsnorm(hidden, self.weight, out, self.eps, delta=delta, rows=rows, write_back=write_back, settled=settled)
+        kernels.add_rmsnorm(hidden, self.weight, out, self.eps, delta=delta, rows=rows, write_back=write_back, settled=settled,
+                            exact=self.exact)
