@@ -3,6 +3,8 @@
     python -m edgerag_b200.ops.microbench decode-attention --batch 8 --context 8192
     python -m edgerag_b200.ops.microbench prefill-attention --tokens 2048
     python -m edgerag_b200.ops.microbench linear --m 8 --n 6144 --k 2048
+    python -m edgerag_b200.ops.microbench latent-attention --batch 8 --context 8192
+    python -m edgerag_b200.ops.microbench ssm-scan --batch 8 --tokens 1
     python -m edgerag_b200.ops.microbench step-kernels --layers 4 --batch 8 --context 8192 --iters 4
 
 Each case builds random inputs larger than the 126 MB L2 where the real workload is (or says that
@@ -294,6 +296,73 @@ def step_timeline(a) -> dict:
             "layer_period_us": round(period, 2), "step_us": round(events[-1].time_range.end - t0, 1), "kernels_of_a_layer": rows}
 
 
+def latent_attention(a) -> dict:
+    """The attention kernel over cache rows [c | kr]: single tokens at the end of ``context`` cached tokens
+    (bound by the rows it reads), or ``tokens`` prompt tokens after ``past`` (bound by its products)."""
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    dk, item = a.rank + a.rot, 2 if dtype == torch.bfloat16 else 4
+    decode = a.tokens <= 0
+    n_seqs = a.batch if decode else 1
+    total = a.context if decode else a.past + a.tokens
+    n = n_seqs if decode else a.tokens
+    pages_per = -(-total // a.page)
+    reps = max(2, int(300e6 // (n_seqs * total * dk * item)) + 1) if (decode and a.cold) else 1
+    pools = [torch.randn((n_seqs * pages_per, 1, a.page, dk), device="cuda").to(dtype) for _ in range(reps)]
+    tables = torch.randperm(n_seqs * pages_per).to(torch.int32).view(n_seqs, pages_per).cuda()
+    q = torch.randn((n, a.heads, dk), device="cuda") * dk ** -0.5
+    out = torch.empty((n, a.heads, a.rank), device="cuda", dtype=dtype)
+    if decode:
+        pos = torch.full((n,), total - 1, dtype=torch.int32, device="cuda")
+        seq_of = torch.arange(n, dtype=torch.int32, device="cuda")
+        blocks = -(-n * a.heads // 4)
+        want = max(1, min(-(-2 * kernels._sms(q.device) // blocks), -(-total // 64)))
+        split = a.split or -(-(-(-total // want)) // 64) * 64
+        n_splits = -(-total // split)
+    else:
+        pos = torch.arange(a.past, total, dtype=torch.int32, device="cuda")
+        seq_of = torch.zeros(n, dtype=torch.int32, device="cuda")
+        split, n_splits = 0, 1
+    part = torch.empty(max(1, kernels.latent_scratch_floats(n, a.heads, a.rank, n_splits)), device="cuda")
+    state = {"i": 0}
+
+    def fn():
+        state["i"] = (state["i"] + 1) % reps
+        kernels.latent_attention(q, pools[state["i"]], tables, seq_of, pos, out, 1.0, 0, n, split_keys=split,
+                                 n_splits=n_splits, part=part if n_splits > 1 else None)
+
+    us = _time(fn, max(a.iters, 2 * reps), a.warmup)
+    nbytes = n_seqs * total * dk * item
+    pairs = n * total if decode else a.tokens * a.past + a.tokens * (a.tokens + 1) / 2
+    flops = 2.0 * a.heads * (dk + a.rank) * pairs
+    return {"case": "latent-attention", "mode": "decode" if decode else "prefill", "splits": n_splits, "us": round(us, 2),
+            "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
+            "tflops": round(flops / us / 1e6, 2), "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4),
+            "from_dram": bool(decode and (a.cold or nbytes > 126e6))}
+
+
+def ssm_scan(a) -> dict:
+    """The recurrence kernel: ``batch`` requests of ``tokens`` tokens each.  One token per request is bound by
+    the state it reads and writes; a prompt portion by the walk along its tokens."""
+    dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
+    inner, ch = a.heads * a.head_dim, a.heads * a.head_dim + 2 * a.groups * a.state
+    n = a.batch * a.tokens
+    xbc = (torch.randn((n, ch), device="cuda") * 0.3).to(dtype)
+    proj = torch.randn((n, a.heads), device="cuda").to(dtype)
+    vec = [torch.randn(a.heads, device="cuda") for _ in range(3)]
+    state = torch.zeros((a.batch, a.heads, a.state, a.head_dim), device="cuda")
+    y = torch.empty((n, inner), device="cuda")
+    starts = (torch.arange(a.batch + 1, dtype=torch.int32) * a.tokens).cuda()
+    slots = torch.arange(a.batch, dtype=torch.int32).cuda()
+    fn = lambda: kernels.ssm_scan(xbc, proj, 0, vec[0], vec[1], vec[2], state, a.batch, starts, slots, y, a.groups)  # noqa: E731
+    us = _time(fn, a.iters, a.warmup)
+    item = 2 if dtype == torch.bfloat16 else 4
+    nbytes = 2 * state.numel() * 4 + n * (ch * item + inner * 4)
+    flops = 6.0 * n * a.heads * a.state * a.head_dim
+    return {"case": "ssm-scan", "us": round(us, 2), "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1),
+            "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4), "gflops": round(flops / us / 1e3, 1),
+            "tokens_per_s": round(n / us * 1e6, 1), "from_dram": nbytes > 126e6}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="edgerag_b200.ops.microbench", description=__doc__.split("\n\n")[0])
     sub = ap.add_subparsers(dest="case", required=True)
@@ -342,12 +411,31 @@ def main(argv=None) -> int:
     t.add_argument("--context", type=int, default=640)
     t.add_argument("--heads", type=int, default=32)
     t.add_argument("--kv-heads", type=int, default=32)
+    la = sub.add_parser("latent-attention", parents=[common])
+    la.add_argument("--heads", type=int, default=16)
+    la.add_argument("--rank", type=int, default=512, help="width of the cached latent")
+    la.add_argument("--rot", type=int, default=64, help="width of the shared rotated key part")
+    la.add_argument("--page", type=int, default=16)
+    la.add_argument("--batch", type=int, default=8)
+    la.add_argument("--context", type=int, default=8192)
+    la.add_argument("--tokens", type=int, default=0, help="prompt tokens (0: single tokens of --batch requests)")
+    la.add_argument("--past", type=int, default=0)
+    la.add_argument("--split", type=int, default=0)
+    la.add_argument("--cold", action="store_true")
+    ss = sub.add_parser("ssm-scan", parents=[common])
+    ss.add_argument("--heads", type=int, default=64)
+    ss.add_argument("--head-dim", type=int, default=64)
+    ss.add_argument("--state", type=int, default=128)
+    ss.add_argument("--groups", type=int, default=8)
+    ss.add_argument("--batch", type=int, default=8)
+    ss.add_argument("--tokens", type=int, default=1)
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():
         print("microbench needs a CUDA device", file=sys.stderr)
         return 1
     fn = {"decode-attention": decode_attention, "prefill-attention": prefill_attention, "linear": linear,
-          "step-kernels": step_kernels, "step-timeline": step_timeline}[a.case]
+          "step-kernels": step_kernels, "step-timeline": step_timeline, "latent-attention": latent_attention,
+          "ssm-scan": ssm_scan}[a.case]
     load_peaks(a.peaks)
     result = fn(a)
     result["peaks"] = PEAKS_FROM
