@@ -494,6 +494,159 @@ def run_reference(args) -> dict:
     }
 
 
+# --- the Dokodra design beside the Llama decoder at equal sizes ------------------------------------
+
+DESIGN_SIZES = {
+    "w1024": {"width": 1024, "ff": 4096, "vocab": 32768,
+              "att": {"heads": 8, "dim": 64, "rot_dim": 32, "vdim": 64, "kv_rank": 256, "q_rank": 768},
+              "ssm": {"heads": 32, "vdim": 64, "state": 64, "groups": 4, "conv": 4, "norm_groups": 4}},
+    "w2048": {"width": 2048, "ff": 8192, "vocab": 32768,
+              "att": {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "q_rank": 1536},
+              "ssm": {"heads": 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}},
+}
+
+
+def dokodra_config(size: dict, n_layers: int) -> dict:
+    """Layers in the order latent attention, state-space mixer (no feed-forward), latent attention with a
+    query latent and sinks, latent attention on the first layer's cache rows; repeated."""
+    att = dict(size["att"])
+    q_rank = att.pop("q_rank")
+    att.update(scale=(att["dim"] + att["rot_dim"]) ** -0.5, rot={"base": 10000.0, "dims": att["rot_dim"]})
+    mlp = {"kind": "dense", "ff": size["ff"], "limit": 7.0}
+    layers = []
+    for i in range(n_layers):
+        kind = i % 4
+        if kind == 1:
+            layers.append({"type": "mamba2", "mixer": dict(size["ssm"]), "mlp": None})
+        elif kind == 2:
+            layers.append({"type": "latent_attention_2", "mixer": dict(att, q_rank=q_rank), "mlp": mlp})
+        elif kind == 3:
+            layers.append({"type": "latent_attention", "mixer": dict(att, kv_from=i - 3), "mlp": mlp})
+        else:
+            layers.append({"type": "latent_attention", "mixer": dict(att), "mlp": mlp})
+    return {"architecture": "Dokodra", "width": size["width"], "vocab": size["vocab"], "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}
+
+
+def llama_config(size: dict, n_layers: int) -> dict:
+    heads = size["width"] // 64
+    return dict(CONFIG_2B, num_hidden_layers=n_layers, hidden_size=size["width"], num_attention_heads=heads,
+                num_key_value_heads=heads, intermediate_size=size["ff"], vocab_size=size["vocab"], rope_theta=10000.0,
+                tie_word_embeddings=False)
+
+
+def run_designs(args) -> dict:
+    """Prefill (one portion of 2,048 tokens) and decode (batch 1 and --batch at a context of 2,048) of Dokodra
+    and of the Llama decoder at the same width, feed-forward size, vocabulary and layer count, random
+    weights, plus the new design's kernels alone against their rooflines."""
+    import types
+
+    import torch
+
+    sys.path.insert(0, str(ROOT))
+    from edgerag_b200.engine.engine import Engine, EngineOptions
+    from edgerag_b200.engine.step import StepEntry
+    from edgerag_b200.ops import kernels, microbench
+
+    torch.cuda.set_device(0)
+    peak, peak_source = peaks()
+    microbench.HBM_GBS, microbench.BF16_TFLOPS = float(peak["hbm_gbs"]), float(peak["bf16_tflops"])
+    n_layers = args.layers if args.layers != CONFIG_2B["num_hidden_layers"] else 8
+    context, prompt, block, k, w = 2048, 2048, 16, args.steps, args.warmup
+    clocks = ClockSampler()
+    gen = torch.Generator().manual_seed(0)
+    out: dict = {}
+
+    def measure(cfg: dict, vocab: int) -> dict:
+        most = max(args.batch, 1)
+        engine = Engine.from_config(cfg, weights_seed=0, std=0.02, options=EngineOptions(
+            dtype="bfloat16", device="cuda:0", block_size=block, num_blocks=(most + 1) * (context // block + 4),
+            max_batch_size=most + 1, chunk_size=prompt, max_step_tokens=prompt + most, max_model_len=context + 64))
+        runner, cache = engine.runner, engine.cache
+        ids = torch.randint(0, vocab, (prompt,), generator=gen).tolist()
+        times = []
+        for i in range(8):
+            runner.admit(f"p{i}")
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            runner.step([StepEntry(f"p{i}", tokens=ids, want=[prompt - 1])])
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            runner.release(f"p{i}")
+        res = {"prefill_ms": round(statistics.median(times[3:]), 3),
+               "prefill_tokens_per_s": round(prompt / (statistics.median(times[3:]) / 1e3), 1)}
+        tokens = torch.empty(256, dtype=torch.int32, device="cuda")
+        for pb in sorted({1, args.batch}):
+            names = [f"d{pb}_{i}" for i in range(pb)]
+            for r in names:
+                runner.admit(r)
+                cache.grow(r, context - 2 * (k + w) - 4)
+                cache.advance(r, context - 2 * (k + w) - 4)
+            toks = torch.randint(0, vocab, (pb,), generator=gen).tolist()
+            step = lambda: kernels.sample_rows(runner.step([StepEntry(r, tokens=[t], want=[0]) for r, t in zip(names, toks)]), tokens)  # noqa: E731
+            for _ in range(w):
+                step()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            sampler = ClockSampler()
+            with sampler:
+                a.record()
+                for _ in range(k):
+                    step()
+                b.record()
+                torch.cuda.synchronize()
+            clocks.merge(sampler)
+            ms = a.elapsed_time(b) / k
+            res[f"decode_b{pb}_ms"] = round(ms, 4)
+            res[f"decode_b{pb}_tokens_per_s"] = round(pb / (ms / 1e3), 1)
+            for r in names:
+                runner.release(r)
+        res["weights_bytes"] = int(sum(t.numel() * t.element_size() for t in _tensors_of(engine.model)))
+        del engine
+        torch.cuda.empty_cache()
+        return res
+
+    for name, size in DESIGN_SIZES.items():
+        out[name] = {"layers": n_layers, "dokodra": measure(dokodra_config(size, n_layers), size["vocab"]),
+                     "llama": measure(llama_config(size, n_layers), size["vocab"])}
+    # the new design's kernels alone, and the like kernels of the Llama decoder, at the w2048 sizes
+    att, ssm = DESIGN_SIZES["w2048"]["att"], DESIGN_SIZES["w2048"]["ssm"]
+    ns = lambda **kw: types.SimpleNamespace(dtype="bfloat16", iters=10, warmup=3, page=block, sequential_pages=False, **kw)  # noqa: E731
+    lat = dict(heads=att["heads"], rank=att["kv_rank"], rot=att["rot_dim"], split=0)
+    kern = {
+        "latent_attention_decode_b8_ctx8192": microbench.latent_attention(ns(batch=8, context=8192, tokens=0, past=0, cold=True, **lat)),
+        "latent_attention_prefill_2048": microbench.latent_attention(ns(batch=1, context=0, tokens=2048, past=0, cold=False, **lat)),
+        "llama_attention_decode_b8_ctx8192": microbench.decode_attention(ns(batch=8, context=8192, heads=32, kv_heads=32, head_dim=64, split=0,
+                                                                            kernel="bulk", head_group=0, cold=True)),
+        "llama_attention_prefill_2048": microbench.prefill_attention(ns(tokens=2048, past=0, heads=32, kv_heads=32, head_dim=64, kernel="tc",
+                                                                        key_splits=0)),
+        "ssm_scan_decode_b8": microbench.ssm_scan(ns(heads=ssm["heads"], head_dim=ssm["vdim"], state=ssm["state"], groups=ssm["groups"],
+                                                     batch=64, tokens=1)),
+        "ssm_scan_prefill_2048": microbench.ssm_scan(ns(heads=ssm["heads"], head_dim=ssm["vdim"], state=ssm["state"], groups=ssm["groups"],
+                                                        batch=1, tokens=2048)),
+    }
+    return {"metric": "design_compare", "unit": "tokens/s", "n_gpus": 1, "steps": k, "warmup": w, "dtype": "bf16",
+            "data": "synthetic", "impl": "ours", "higher_is_better": True,
+            "config": {"designs": ["Dokodra", "Llama decoder"], "prefill_tokens": prompt, "decode_context": context,
+                       "decode_batches": sorted({1, args.batch}), "page_tokens": block, "peaks": peak_source,
+                       "l2": "decode: weights and cache larger than L2 at w2048; kernels: caches rotated (cold)"},
+            "sizes": out, "kernels": kern, "clocks": clocks.record()}
+
+
+def _tensors_of(model) -> list:
+    import torch
+
+    seen, found = set(), []
+    for _, part in model._owners:
+        for v in vars(part).values():
+            if isinstance(v, torch.Tensor) and v.data_ptr() not in seen:
+                seen.add(v.data_ptr())
+                found.append(v)
+    return found
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--gpus", type=int, default=1)
@@ -505,9 +658,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=CONFIG_2B["num_hidden_layers"],
                     help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
-    ap.add_argument("--workload", choices=["decode", "mixed", "continuous"], default="decode",
+    ap.add_argument("--workload", choices=["decode", "mixed", "continuous", "designs"], default="decode",
                     help="decode: the headline measurement; mixed / continuous: the serving workloads of the "
-                         "256M and 500M decoders through Engine.generate")
+                         "256M and 500M decoders through Engine.generate; designs: prefill and decode of the Dokodra "
+                         "design beside the Llama decoder at equal sizes, and its kernels against their rooflines")
     ap.add_argument("--ref-cpu-check", action="store_true",
                     help="with --impl reference: a dry run of the reference arm's loop at toy sizes on the CPU")
     args = ap.parse_args()
@@ -518,6 +672,8 @@ def main() -> int:
         args.warmup = 3
     if args.impl == "reference":
         result = run_reference(args)
+    elif args.workload == "designs":
+        result = run_designs(args)
     elif args.workload != "decode":
         result = run_serving_workload(args)
     else:

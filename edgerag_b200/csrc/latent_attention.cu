@@ -253,6 +253,263 @@ latent_combine_kernel(const float* __restrict__ part, const T* __restrict__ gate
   }
 }
 
+#if ERB_ELEM == 1
+// ---------------------------------------------------------------------------------------------
+// The same attention on tensor cores (bfloat16): a block owns M = 16 * MT neighbouring (token, head) rows of
+// one sequence and walks the sequence's cache rows in tiles of 64 keys, which arrive by 16-byte
+// asynchronous copies straight from the pages into one of two stages of shared memory (keys past the
+// end are filled with zeros).  Per tile: warp w makes the scores of the tile's keys 8w .. 8w + 7 for all M
+// rows (mma.sync m16n8k16, queries and keys by ldmatrix, float accumulation over the whole cache row);
+// maxima and sums of a row are exchanged through shared memory, the weights go there as bfloat16; then
+// every warp adds  P [M x 64] . C [64 x its NT * 8 columns of the latent]  to its float accumulators, the
+// latent read from the same stage by ldmatrix.trans.  Queries are scaled, rounded to bfloat16 and kept in
+// shared memory for the whole walk.  Splits, sink and gate are those of the kernel above.
+// ---------------------------------------------------------------------------------------------
+constexpr int kMmaWarps = 8;
+constexpr int kMmaKeys = 64;
+constexpr int kMmaPStride = kMmaKeys + 8;
+
+__device__ __forceinline__ void ldsm4(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4t(uint32_t* r, const void* p) {
+  const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+  const int bytes = real ? 16 : 0;                           // 0 bytes read: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+
+template <int MT, int NT>
+__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16* __restrict__ pages,
+                            const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
+                            const int* __restrict__ positions, const __nv_bfloat16* __restrict__ gate, int gate_ld,
+                            const float* __restrict__ sink, __nv_bfloat16* __restrict__ out, float* __restrict__ part,
+                            int first_token, int seq0, int n_seqs, int H, int R, int Dk, int page_size, int split_keys,
+                            int n_splits, float scale) {
+  chain_wait();
+  constexpr int M = 16 * MT;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int D16 = (Dk + 15) & ~15, DkP = D16 + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [M][DkP]
+  __nv_bfloat16* Ks = Qs + M * DkP;                                      // [2][64][DkP]
+  __nv_bfloat16* Ps = Ks + 2 * kMmaKeys * DkP;                           // [M][72]
+  float* red_max = reinterpret_cast<float*>(Ps + M * kMmaPStride);       // [warps][M]
+  float* red_sum = red_max + kMmaWarps * M;                              // [warps][M]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
+
+  // which sequence, which of its row tiles
+  int tile = blockIdx.x, s = seq0, rows_s = 0;
+  for (;; ++s) {
+    if (s >= seq0 + n_seqs) return;
+    rows_s = (seq_starts[s + 1] - seq_starts[s]) * H;
+    const int tiles = (rows_s + M - 1) / M;
+    if (tile < tiles) break;
+    tile -= tiles;
+  }
+  const int tok0 = seq_starts[s], r0 = tile * M;
+  const int valid = min(M, rows_s - r0);
+  const int pos_max = positions[tok0 + (r0 + valid - 1) / H];
+  const int split = blockIdx.y;
+  const int begin = n_splits > 1 ? split * split_keys : 0;
+  const int end = n_splits > 1 ? min(pos_max + 1, begin + split_keys) : pos_max + 1;
+  const int* bt = block_tables + (size_t)s * max_pages;
+
+  // queries: scaled, rounded, zero beyond the valid rows and beyond Dk
+  const float* q_rows = q_lat + ((size_t)tok0 * H + r0) * Dk;
+  for (int idx = threadIdx.x; idx < M * (D16 / 2); idx += blockDim.x) {
+    const int r = idx / (D16 / 2), c = 2 * (idx % (D16 / 2));
+    float2 v = make_float2(0.f, 0.f);
+    if (r < valid && c < Dk) v = *reinterpret_cast<const float2*>(q_rows + (size_t)r * Dk + c);
+    *reinterpret_cast<__nv_bfloat162*>(Qs + r * DkP + c) = __floats2bfloat162_rn(v.x * scale, v.y * scale);
+  }
+  if (D16 > Dk) {          // the copies never touch these columns
+    for (int idx = threadIdx.x; idx < 2 * kMmaKeys * (D16 - Dk); idx += blockDim.x)
+      Ks[(idx / (D16 - Dk)) * DkP + Dk + idx % (D16 - Dk)] = __float2bfloat16_rn(0.f);
+  }
+
+  int pos_r[MT][2];
+  float m_r[MT][2], l_r[MT][2];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int r = 16 * mt + g + 8 * j;
+      pos_r[mt][j] = r < valid ? positions[tok0 + (r0 + r) / H] : -1;
+      m_r[mt][j] = -INFINITY;
+      l_r[mt][j] = 0.f;
+    }
+  float o[MT][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o[mt][nt][i] = 0.f;
+
+  const int chunks_per_row = Dk / 8;
+  auto load_tile = [&](int k0, int stage) {
+    __nv_bfloat16* dst = Ks + stage * kMmaKeys * DkP;
+    for (int idx = threadIdx.x; idx < kMmaKeys * chunks_per_row; idx += blockDim.x) {
+      const int r = idx / chunks_per_row, c = (idx % chunks_per_row) * 8;
+      const int k = k0 + r;
+      const bool real = k < end;
+      const __nv_bfloat16* src = pages;
+      if (real) src = pages + ((size_t)bt[k / page_size] * page_size + k % page_size) * Dk + c;
+      copy16(dst + r * DkP + c, src, real);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+  const int n_tiles = begin < end ? (end - begin + kMmaKeys - 1) / kMmaKeys : 0;
+  if (n_tiles > 0) load_tile(begin, 0);
+  for (int it = 0; it < n_tiles; ++it) {
+    const int k0 = begin + it * kMmaKeys, stage = it & 1;
+    if (it + 1 < n_tiles) {
+      load_tile(k0 + kMmaKeys, stage ^ 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const __nv_bfloat16* Kt = Ks + stage * kMmaKeys * DkP;
+
+    // scores of keys 8 * warp .. + 7 for all rows
+    float sc[MT][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[mt][i] = 0.f;
+    for (int kk = 0; kk < D16; kk += 32) {
+      uint32_t b[4];
+      ldsm4(b, Kt + (8 * warp + (lane & 7)) * DkP + kk + 8 * (lane >> 3));
+      const bool second = kk + 16 < D16;
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        uint32_t a[4];
+        const __nv_bfloat16* qa = Qs + (16 * mt + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + kk + 8 * (lane >> 4);
+        ldsm4(a, qa);
+        mma16816(sc[mt], a, b[0], b[1]);
+        if (second) {
+          ldsm4(a, qa + 16);
+          mma16816(sc[mt], a, b[2], b[3]);
+        }
+      }
+    }
+    const int key0 = k0 + 8 * warp + 2 * tq;
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int lim = min(pos_r[mt][j], end - 1);
+        if (key0 > lim) sc[mt][2 * j] = -INFINITY;
+        if (key0 + 1 > lim) sc[mt][2 * j + 1] = -INFINITY;
+        float mx = fmaxf(sc[mt][2 * j], sc[mt][2 * j + 1]);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        if (tq == 0) red_max[warp * M + 16 * mt + g + 8 * j] = mx;
+      }
+    __syncthreads();
+    float alpha[MT][2];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int r = 16 * mt + g + 8 * j;
+        float top = m_r[mt][j];
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, red_max[w * M + r]);
+        const bool none = top == -INFINITY;
+        alpha[mt][j] = (none || m_r[mt][j] == -INFINITY) ? (none ? 1.f : 0.f) : __expf(m_r[mt][j] - top);
+        const float p0 = (none || sc[mt][2 * j] == -INFINITY) ? 0.f : __expf(sc[mt][2 * j] - top);
+        const float p1 = (none || sc[mt][2 * j + 1] == -INFINITY) ? 0.f : __expf(sc[mt][2 * j + 1] - top);
+        *reinterpret_cast<__nv_bfloat162*>(Ps + r * kMmaPStride + 8 * warp + 2 * tq) = __floats2bfloat162_rn(p0, p1);
+        float ps = p0 + p1;
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        if (tq == 0) red_sum[warp * M + r] = ps;
+        m_r[mt][j] = top;
+      }
+    __syncthreads();
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int r = 16 * mt + g + 8 * j;
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; ++w) sum += red_sum[w * M + r];
+        l_r[mt][j] = l_r[mt][j] * alpha[mt][j] + sum;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          o[mt][nt][2 * j] *= alpha[mt][j];
+          o[mt][nt][2 * j + 1] *= alpha[mt][j];
+        }
+      }
+    // O += P . C for this warp's columns
+#pragma unroll
+    for (int ks = 0; ks < kMmaKeys / 16; ++ks) {
+      uint32_t a[MT][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+        ldsm4(a[mt], Ps + (16 * mt + (lane & 7) + 8 * ((lane >> 3) & 1)) * kMmaPStride + 16 * ks + 8 * (lane >> 4));
+#pragma unroll
+      for (int pr = 0; pr < NT / 2; ++pr) {
+        const int n0 = (warp * NT + 2 * pr) * 8;
+        if (n0 < R) {
+          uint32_t b[4];
+          ldsm4t(b, Kt + (16 * ks + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + n0 + 8 * (lane >> 4));
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma16816(o[mt][2 * pr], a[mt], b[0], b[1]);
+            mma16816(o[mt][2 * pr + 1], a[mt], b[2], b[3]);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int r = 16 * mt + g + 8 * j;
+      if (r >= valid) continue;
+      const int tok = tok0 + (r0 + r) / H, h = (r0 + r) % H;
+      if (n_splits > 1) {
+        float* dst = part + ((size_t)((tok - first_token) * H + h) * n_splits + split) * (R + 2);
+        if (warp == 0 && tq == 0) { dst[0] = m_r[mt][j]; dst[1] = l_r[mt][j]; }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int c = (warp * NT + nt) * 8 + 2 * tq;
+          if (c < R) { dst[2 + c] = o[mt][nt][2 * j]; dst[3 + c] = o[mt][nt][2 * j + 1]; }
+        }
+      } else {
+        const float f = finish_factor(m_r[mt][j], l_r[mt][j], sink, h,
+                                      gate ? __bfloat162float(gate[(size_t)tok * gate_ld + h]) : 0.f, gate != nullptr);
+        __nv_bfloat16* dst = out + ((size_t)tok * H + h) * R;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int c = (warp * NT + nt) * 8 + 2 * tq;
+          if (c < R) *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(o[mt][nt][2 * j] * f, o[mt][nt][2 * j + 1] * f);
+        }
+      }
+    }
+}
+#endif  // ERB_ELEM == 1
+
 template <int NI>
 void launch_attention(dim3 grid, cudaStream_t stream, const float* q_lat, const elem_t* pages, const int* block_tables,
                       int max_pages, const int* seq_of_token, const int* positions, const elem_t* gate, int gate_ld,
@@ -316,5 +573,53 @@ ERB_EXPORT int erb_latent_attention(const float* q_lat, const void* pages, const
   if (rc || n_splits == 1) return rc;
   launch_chained(latent_combine_kernel<elem_t>, dim3(n_rows), dim3(128), 0, st, (const float*)part, (const elem_t*)gate, gate_ld,
                  sink, (elem_t*)out, first_token, H, R, n_splits);
+  return check_launch("latent_combine");
+}
+
+// The tensor-core form (bfloat16 build only): sequences seq0 .. seq0 + n_seqs of the batch, whose rows are
+// tokens seq_starts[s] .. seq_starts[s + 1]; `n_tiles` = sum over them of ceil(tokens * H / (16 * mt)).
+// Needs cache rows and latents of a multiple of 8 entries (16-byte copies, whole column tiles), R <= 512.
+ERB_EXPORT int erb_latent_attention_mma(const float* q_lat, const void* pages, const int* block_tables, int max_pages,
+                                        const int* seq_starts, const int* positions, const void* gate, int gate_ld,
+                                        const float* sink, void* out, float* part, int first_token, int seq0, int n_seqs,
+                                        int n_tiles, int mt, int H, int R, int dr, int page_size, int split_keys,
+                                        int n_splits, float scale, void* stream) {
+#if ERB_ELEM == 1
+  if (n_seqs <= 0 || n_tiles <= 0) return ERB_OK;
+  const int Dk = R + dr;
+  if (H <= 0 || R <= 0 || R % 8 || Dk % 8 || R > 512 || page_size <= 0 || n_splits < 1 || (mt != 1 && mt != 2) ||
+      ((uintptr_t)pages & 15) || (n_splits > 1 && (!part || split_keys <= 0 || split_keys % kMmaKeys)))
+    return fail(ERB_ERR_UNSUPPORTED, "latent_attention_mma: sizes (latent %d, row %d) or alignment not supported", R, Dk);
+  const int D16 = (Dk + 15) & ~15, DkP = D16 + 8, M = 16 * mt;
+  const size_t smem = sizeof(__nv_bfloat16) * ((size_t)M * DkP + 2 * kMmaKeys * DkP + M * kMmaPStride) +
+                      sizeof(float) * 2 * kMmaWarps * M;
+  if (smem > 227 * 1024) return fail(ERB_ERR_UNSUPPORTED, "latent_attention_mma: rows of %d entries need %zu bytes", Dk, smem);
+  const int nt = (R / 8 + kMmaWarps - 1) / kMmaWarps;
+  const dim3 grid(n_tiles, n_splits);
+  cudaStream_t st = (cudaStream_t)stream;
+#define ERB_LAT_MMA(MT_, NT_)                                                                                             \
+  do {                                                                                                                    \
+    auto kern = latent_attention_mma_kernel<MT_, NT_>;                                                                    \
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "latent_attention_mma: %s", cudaGetErrorString(e));                   \
+    launch_chained(kern, grid, dim3(kMmaWarps * 32), smem, st, q_lat, (const __nv_bfloat16*)pages, block_tables, max_pages, \
+                   seq_starts, positions, (const __nv_bfloat16*)gate, gate_ld, sink, (__nv_bfloat16*)out, part, first_token, \
+                   seq0, n_seqs, H, R, Dk, page_size, split_keys, n_splits, scale);                                       \
+  } while (0)
+  if (mt == 1) { if (nt <= 2) ERB_LAT_MMA(1, 2); else if (nt <= 4) ERB_LAT_MMA(1, 4); else ERB_LAT_MMA(1, 8); }
+  else { if (nt <= 2) ERB_LAT_MMA(2, 2); else if (nt <= 4) ERB_LAT_MMA(2, 4); else ERB_LAT_MMA(2, 8); }
+#undef ERB_LAT_MMA
+  return check_launch("latent_attention_mma");
+#else
+  return fail(ERB_ERR_UNSUPPORTED, "latent_attention_mma: built for bfloat16 only");
+#endif
+}
+
+// Merge of the splits that the tensor-core form left for `n_tokens` tokens from `first_token` on.
+ERB_EXPORT int erb_latent_combine(const float* part, const void* gate, int gate_ld, const float* sink, void* out,
+                                  int first_token, int n_tokens, int H, int R, int n_splits, void* stream) {
+  if (n_tokens <= 0) return ERB_OK;
+  launch_chained(latent_combine_kernel<elem_t>, dim3(n_tokens * H), dim3(128), 0, (cudaStream_t)stream, part, (const elem_t*)gate,
+                 gate_ld, sink, (elem_t*)out, first_token, H, R, n_splits);
   return check_launch("latent_combine");
 }

@@ -142,6 +142,83 @@ ssm_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
     if (i < NL && n0 + i < N) s_glob[(size_t)(n0 + i) * P + p] = S[i];
 }
 
+// The same scan for states whose row count is a multiple of 16: a block owns PB (16 or 32) columns of one
+// head's state, thread (l, p) rows 16 l .. 16 l + 15 of column p, so a head gives P / PB blocks of N / 16 * PB
+// light threads (more blocks in flight, and a warp reads B and C as 16-byte broadcasts).  Same arithmetic in
+// the same order per state entry; the partial sums of a column are added in the order of l.
+template <typename T>
+__global__ void __launch_bounds__(512)
+ssm_scan16_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ proj, int ld, int off_dt,
+                  const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
+                  float* __restrict__ state, const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
+                  float* __restrict__ y, int H, int P, int N, int G, int PB) {
+  chain_wait();
+  constexpr int NL = 16;
+  extern __shared__ __align__(16) float smem[];
+  const int L = N / NL;
+  float* b_s = smem;                                   // [chunk][N]
+  float* c_s = b_s + kScanChunk * N;                   // [chunk][N]
+  float* x_s = c_s + kScanChunk * N;                   // [chunk][PB]
+  float* dt_s = x_s + kScanChunk * PB;                 // [chunk]
+  float* decay_s = dt_s + kScanChunk;                  // [chunk]
+  float* part_s = decay_s + kScanChunk;                // [chunk][L][PB]
+  const int h = blockIdx.x, seq = blockIdx.y, p0 = blockIdx.z * PB;
+  const int g = h / (H / G);
+  const int inner = H * P;
+  const int p = threadIdx.x % PB, l = threadIdx.x / PB;
+  const int n0 = l * NL;
+  const int start = seq_starts[seq], n_tok = seq_starts[seq + 1] - start;
+  float* s_glob = state + (((size_t)state_slots[seq] * H + h) * N + n0) * P + p0 + p;
+  float S[NL];
+#pragma unroll
+  for (int i = 0; i < NL; ++i) S[i] = s_glob[(size_t)i * P];
+  const float a = -expf(a_log[h]), bias = dt_bias[h], dskip = d_skip[h];
+  for (int c0 = 0; c0 < n_tok; c0 += kScanChunk) {
+    const int nc = min(kScanChunk, n_tok - c0);
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nc * N; idx += blockDim.x) {
+      const int k = idx / N, n = idx % N;
+      const T* row = xbc + (size_t)(start + c0 + k) * channels;
+      b_s[idx] = Elem<T>::load(row + inner + g * N + n);
+      c_s[idx] = Elem<T>::load(row + inner + G * N + g * N + n);
+    }
+    for (int idx = threadIdx.x; idx < nc * PB; idx += blockDim.x) {
+      const int k = idx / PB, pp = idx % PB;
+      x_s[idx] = Elem<T>::load(xbc + (size_t)(start + c0 + k) * channels + h * P + p0 + pp);
+    }
+    for (int k = threadIdx.x; k < nc; k += blockDim.x) {
+      const float dt = softplus_f(Elem<T>::load(proj + (size_t)(start + c0 + k) * ld + off_dt + h) + bias);
+      dt_s[k] = dt;
+      decay_s[k] = expf(a * dt);
+    }
+    __syncthreads();
+    for (int k = 0; k < nc; ++k) {
+      const float decay = decay_s[k], dx = dt_s[k] * x_s[k * PB + p];
+      const float4* bk = reinterpret_cast<const float4*>(b_s + k * N + n0);
+      const float4* ck = reinterpret_cast<const float4*>(c_s + k * N + n0);
+      float sum = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < NL / 4; ++i4) {
+        const float4 b = bk[i4], c = ck[i4];
+        S[4 * i4] = fmaf(decay, S[4 * i4], b.x * dx);         sum = fmaf(S[4 * i4], c.x, sum);
+        S[4 * i4 + 1] = fmaf(decay, S[4 * i4 + 1], b.y * dx); sum = fmaf(S[4 * i4 + 1], c.y, sum);
+        S[4 * i4 + 2] = fmaf(decay, S[4 * i4 + 2], b.z * dx); sum = fmaf(S[4 * i4 + 2], c.z, sum);
+        S[4 * i4 + 3] = fmaf(decay, S[4 * i4 + 3], b.w * dx); sum = fmaf(S[4 * i4 + 3], c.w, sum);
+      }
+      part_s[(k * L + l) * PB + p] = sum;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < nc * PB; idx += blockDim.x) {
+      const int k = idx / PB, pp = idx % PB;
+      float sum = 0.f;
+      for (int ll = 0; ll < L; ++ll) sum += part_s[(k * L + ll) * PB + pp];
+      y[(size_t)(start + c0 + k) * inner + h * P + p0 + pp] = sum + dskip * x_s[idx];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NL; ++i) s_glob[(size_t)i * P] = S[i];
+}
+
 // One block per (token, part): out = unit_rms(y * silu(z)) * weight over the part's entries.  `gate` may
 // be null (no gate), `x` is float (X32) or T.
 template <typename T, bool X32>
@@ -193,6 +270,18 @@ ERB_EXPORT int erb_ssm_scan(const void* xbc, int channels, const void* proj, int
                             const int* state_slots, float* y, int n_seqs, int H, int P, int N, int G, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
   if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G || P > 512) return fail(ERB_ERR_ARG, "ssm_scan: bad sizes (columns of at most 512)");
+  const int PB = P % 32 == 0 ? 32 : (P % 16 == 0 ? 16 : 0);
+  if (PB && N % 16 == 0 && (N / 16) * PB <= 512) {
+    const size_t smem16 = sizeof(float) * ((size_t)kScanChunk * (2 * N + PB + 2 + (size_t)(N / 16) * PB));
+    if (smem16 > 48 * 1024) {
+      cudaError_t e = cudaFuncSetAttribute(ssm_scan16_kernel<elem_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem16);
+      if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "ssm_scan: %s", cudaGetErrorString(e));
+    }
+    launch_chained(ssm_scan16_kernel<elem_t>, dim3(H, n_seqs, P / PB), dim3((N / 16) * PB), smem16, (cudaStream_t)stream,
+                   (const elem_t*)xbc, channels, (const elem_t*)proj, ld, off_dt, dt_bias, a_log, d_skip, state, seq_starts,
+                   state_slots, y, H, P, N, G, PB);
+    return check_launch("ssm_scan");
+  }
   int L = 512 / P;                       // threads that share a column of the state
   if (L > 4) L = 4;
   if (L > N) L = N;

