@@ -614,7 +614,7 @@ def run_designs(args) -> dict:
     # the new design's kernels alone, and the like kernels of the Llama decoder, at the w2048 sizes
     att, ssm = DESIGN_SIZES["w2048"]["att"], DESIGN_SIZES["w2048"]["ssm"]
     ns = lambda **kw: types.SimpleNamespace(dtype="bfloat16", iters=10, warmup=3, page=block, sequential_pages=False, **kw)  # noqa: E731
-    lat = dict(heads=att["heads"], rank=att["kv_rank"], rot=att["rot_dim"], split=0)
+    lat = dict(heads=att["heads"], rank=att["kv_rank"], rot=att["rot_dim"], split=0, kernel="mma")
     kern = {
         "latent_attention_decode_b8_ctx8192": microbench.latent_attention(ns(batch=8, context=8192, tokens=0, past=0, cold=True, **lat)),
         "latent_attention_prefill_2048": microbench.latent_attention(ns(batch=1, context=0, tokens=2048, past=0, cold=False, **lat)),

@@ -226,29 +226,41 @@ latent_attention_kernel(const float* __restrict__ q_lat, const T* __restrict__ p
 }
 
 // One block per row: the splits' states merged in split order (a split the row does not reach has l = 0).
+// The splits' maxima and denominators are fetched by one thread each; every split's weight exp(m_s - m) is
+// taken once and shared.  At most kCombineSplits splits.
+constexpr int kCombineSplits = 128;
 template <typename T>
 __global__ void __launch_bounds__(128)
 latent_combine_kernel(const float* __restrict__ part, const T* __restrict__ gate, int gate_ld, const float* __restrict__ sink,
                       T* __restrict__ out, int first_token, int H, int R, int n_splits) {
   chain_wait();
+  __shared__ float m_s[kCombineSplits], l_s[kCombineSplits], weight[kCombineSplits];
   const int row = blockIdx.x;
   const int t = first_token + row / H, h = row % H;
-  const float* src = part + (size_t)row * n_splits * (R + 2);
-  float m = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, src[(size_t)s * (R + 2)]);
-  float l = 0.f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ms = src[(size_t)s * (R + 2)];
-    if (ms != -INFINITY) l += src[(size_t)s * (R + 2) + 1] * expf(ms - m);
+  const size_t stride = (size_t)(R + 2);
+  const float* src = part + (size_t)row * n_splits * stride;
+  float l_mine = 0.f;
+  if ((int)threadIdx.x < n_splits) {
+    m_s[threadIdx.x] = src[threadIdx.x * stride];
+    l_mine = src[threadIdx.x * stride + 1];
   }
+  __syncthreads();
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, m_s[s]);
+  if ((int)threadIdx.x < n_splits) {
+    const float w = m_s[threadIdx.x] == -INFINITY ? 0.f : expf(m_s[threadIdx.x] - m);
+    weight[threadIdx.x] = w;
+    l_s[threadIdx.x] = l_mine * w;
+  }
+  __syncthreads();
+  float l = 0.f;
+  for (int s = 0; s < n_splits; ++s) l += l_s[s];
   const float f = finish_factor(m, l, sink, h, gate ? Elem<T>::load(gate + (size_t)t * gate_ld + h) : 0.f, gate != nullptr);
   T* o = out + ((size_t)t * H + h) * R;
   for (int e = threadIdx.x; e < R; e += blockDim.x) {
     float sum = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ms = src[(size_t)s * (R + 2)];
-      if (ms != -INFINITY) sum += src[(size_t)s * (R + 2) + 2 + e] * expf(ms - m);
-    }
+#pragma unroll 8
+    for (int s = 0; s < n_splits; ++s) sum = fmaf(src[s * stride + 2 + e], weight[s], sum);
     Elem<T>::store(o + e, sum * f);
   }
 }
@@ -556,8 +568,9 @@ ERB_EXPORT int erb_latent_attention(const float* q_lat, const void* pages, const
                                     int dr, int page_size, int split_keys, int n_splits, float scale, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   const int Dk = R + dr;
-  if (H <= 0 || R <= 0 || R % 2 || dr % 2 || page_size <= 0 || n_splits < 1 || (n_splits > 1 && (!part || split_keys <= 0)))
-    return fail(ERB_ERR_ARG, "latent_attention: bad sizes (latent and rotated widths must be even)");
+  if (H <= 0 || R <= 0 || R % 2 || dr % 2 || page_size <= 0 || n_splits < 1 || n_splits > kCombineSplits ||
+      (n_splits > 1 && (!part || split_keys <= 0)))
+    return fail(ERB_ERR_ARG, "latent_attention: bad sizes (latent and rotated widths must be even, at most %d splits)", kCombineSplits);
   if (Dk > 640) return fail(ERB_ERR_UNSUPPORTED, "latent_attention: cache rows of %d entries (at most 640)", Dk);
   const int n_rows = n_tokens * H;
   const dim3 grid((n_rows + kLatWarps - 1) / kLatWarps, n_splits);
@@ -619,6 +632,7 @@ ERB_EXPORT int erb_latent_attention_mma(const float* q_lat, const void* pages, c
 ERB_EXPORT int erb_latent_combine(const float* part, const void* gate, int gate_ld, const float* sink, void* out,
                                   int first_token, int n_tokens, int H, int R, int n_splits, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
+  if (n_splits < 1 || n_splits > kCombineSplits) return fail(ERB_ERR_ARG, "latent_combine: 1 to %d splits", kCombineSplits);
   launch_chained(latent_combine_kernel<elem_t>, dim3(n_tokens * H), dim3(128), 0, (cudaStream_t)stream, part, (const elem_t*)gate,
                  gate_ld, sink, (elem_t*)out, first_token, H, R, n_splits);
   return check_launch("latent_combine");

@@ -35,7 +35,7 @@ conv_silu_kernel(const T* __restrict__ proj, int ld, int off, int channels, int 
   const int start = seq_starts[seq];
   const int i = t - start;                                    // index of the token inside its portion
   const float* old = conv_state + (size_t)state_slots[seq] * (taps - 1) * channels;
-  for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
+  for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < channels; ch += gridDim.y * blockDim.x) {
     float acc = bias ? Elem<T>::load(bias + ch) : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int r = i - (taps - 1 - j);                        // portion index of the input under tap j
@@ -57,7 +57,7 @@ conv_state_update_kernel(const T* __restrict__ proj, int ld, int off, int channe
   const int start = seq_starts[seq], n = seq_starts[seq + 1] - start;
   const int K = taps - 1;
   float* st = conv_state + (size_t)state_slots[seq] * K * channels;
-  for (int ch = threadIdx.x; ch < channels; ch += blockDim.x) {
+  for (int ch = blockIdx.y * blockDim.x + threadIdx.x; ch < channels; ch += gridDim.y * blockDim.x) {
     for (int k = 0; k < K; ++k) {                             // rising k: entry k + n is read before it is written
       const int src = k + n;
       st[(size_t)k * channels + ch] = src < K ? st[(size_t)src * channels + ch]
@@ -251,7 +251,7 @@ ERB_EXPORT int erb_conv_silu(const void* proj, int n_tokens, int ld, int off, in
                              const int* state_slots, void* out, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   if (channels <= 0 || taps < 1 || (taps > 1 && !conv_state)) return fail(ERB_ERR_ARG, "conv_silu: bad sizes");
-  launch_chained(conv_silu_kernel<elem_t>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, (const elem_t*)proj, ld, off,
+  launch_chained(conv_silu_kernel<elem_t>, dim3(n_tokens, n_tokens < 64 ? (channels + 255) / 256 : 1), dim3(256), 0, (cudaStream_t)stream, (const elem_t*)proj, ld, off,
                  channels, taps, (const elem_t*)weight, (const elem_t*)bias, conv_state, seq_of_token, seq_starts, state_slots,
                  (elem_t*)out);
   return check_launch("conv_silu");
@@ -260,7 +260,7 @@ ERB_EXPORT int erb_conv_silu(const void* proj, int n_tokens, int ld, int off, in
 ERB_EXPORT int erb_conv_state_update(const void* proj, int n_seqs, int ld, int off, int channels, int taps, float* conv_state,
                                      const int* seq_starts, const int* state_slots, void* stream) {
   if (n_seqs <= 0 || taps <= 1) return ERB_OK;
-  launch_chained(conv_state_update_kernel<elem_t>, dim3(n_seqs), dim3(256), 0, (cudaStream_t)stream, (const elem_t*)proj, ld,
+  launch_chained(conv_state_update_kernel<elem_t>, dim3(n_seqs, (channels + 255) / 256), dim3(256), 0, (cudaStream_t)stream, (const elem_t*)proj, ld,
                  off, channels, taps, conv_state, seq_starts, state_slots);
   return check_launch("conv_state_update");
 }

@@ -680,6 +680,7 @@ def latent_attention(q_lat: torch.Tensor, pages: torch.Tensor, block_tables: tor
 
 
 LATENT_MMA_KEYS = 64       # keys per tile of the tensor-core form: splits are multiples of it
+LATENT_MAX_SPLITS = 64     # splits a row's keys are cut into at most (the merge kernel takes up to 128)
 
 
 def latent_mma_supported(dtype: torch.dtype, rank: int, rot_dim: int) -> bool:

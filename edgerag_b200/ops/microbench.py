@@ -315,7 +315,7 @@ def latent_attention(a) -> dict:
         pos = torch.full((n,), total - 1, dtype=torch.int32, device="cuda")
         seq_of = torch.arange(n, dtype=torch.int32, device="cuda")
         blocks = -(-n * a.heads // 4)
-        want = max(1, min(-(-2 * kernels._sms(q.device) // blocks), -(-total // 64)))
+        want = max(1, min(-(-2 * kernels._sms(q.device) // blocks), -(-total // 64), kernels.LATENT_MAX_SPLITS))
         split = a.split or -(-(-(-total // want)) // 64) * 64
         n_splits = -(-total // split)
     else:
@@ -325,16 +325,32 @@ def latent_attention(a) -> dict:
     part = torch.empty(max(1, kernels.latent_scratch_floats(n, a.heads, a.rank, n_splits)), device="cuda")
     state = {"i": 0}
 
+    mma = a.kernel == "mma" and kernels.latent_mma_supported(dtype, a.rank, a.rot)
+    if mma:
+        mt = 2 if (not decode or a.heads > 16) else 1
+        q_lens = [1] * n if decode else [a.tokens]
+        tiles = kernels.latent_mma_tiles(q_lens, a.heads, mt)
+        starts = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+        if decode and not a.split:
+            want = max(1, min(-(-kernels._sms(q.device) // tiles), -(-total // 64), kernels.LATENT_MAX_SPLITS))
+            split = -(-(-(-total // want)) // 64) * 64
+            n_splits = -(-total // split)
+            part = torch.empty(max(1, kernels.latent_scratch_floats(n, a.heads, a.rank, n_splits)), device="cuda")
+
     def fn():
         state["i"] = (state["i"] + 1) % reps
-        kernels.latent_attention(q, pools[state["i"]], tables, seq_of, pos, out, 1.0, 0, n, split_keys=split,
-                                 n_splits=n_splits, part=part if n_splits > 1 else None)
+        if mma:
+            kernels.latent_attention_mma(q, pools[state["i"]], tables, starts, pos, out, 1.0, 0, n_seqs, 0, n, tiles, mt,
+                                         split_keys=split, n_splits=n_splits, part=part if n_splits > 1 else None)
+        else:
+            kernels.latent_attention(q, pools[state["i"]], tables, seq_of, pos, out, 1.0, 0, n, split_keys=split,
+                                     n_splits=n_splits, part=part if n_splits > 1 else None)
 
     us = _time(fn, max(a.iters, 2 * reps), a.warmup)
     nbytes = n_seqs * total * dk * item
     pairs = n * total if decode else a.tokens * a.past + a.tokens * (a.tokens + 1) / 2
     flops = 2.0 * a.heads * (dk + a.rank) * pairs
-    return {"case": "latent-attention", "mode": "decode" if decode else "prefill", "splits": n_splits, "us": round(us, 2),
+    return {"case": "latent-attention", "kernel": "mma" if mma else "general", "mode": "decode" if decode else "prefill", "splits": n_splits, "us": round(us, 2),
             "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
             "tflops": round(flops / us / 1e6, 2), "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4),
             "from_dram": bool(decode and (a.cold or nbytes > 126e6))}
@@ -422,6 +438,7 @@ def main(argv=None) -> int:
     la.add_argument("--past", type=int, default=0)
     la.add_argument("--split", type=int, default=0)
     la.add_argument("--cold", action="store_true")
+    la.add_argument("--kernel", choices=["mma", "general"], default="mma", help="tensor cores (bfloat16) or the general kernel")
     ss = sub.add_parser("ssm-scan", parents=[common])
     ss.add_argument("--heads", type=int, default=64)
     ss.add_argument("--head-dim", type=int, default=64)

@@ -103,7 +103,7 @@ class LatentAttention(Mixer):
         """(keys per split, splits) for the single-token rows: enough blocks for ``waves`` blocks per SM, splits
         of a multiple of 64 keys at multiples of their size; a function of the row count and the context bound alone."""
         bound = max(1, ctx.max_keys_bound())
-        want = max(1, min(-(-waves * kernels._sms(self.device) // max(1, n_blocks)), -(-bound // 64)))
+        want = max(1, min(-(-waves * kernels._sms(self.device) // max(1, n_blocks)), -(-bound // 64), kernels.LATENT_MAX_SPLITS))
         split = -(-(-(-bound // want)) // 64) * 64
         return split, -(-bound // split)
 
