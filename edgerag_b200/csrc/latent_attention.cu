@@ -271,13 +271,14 @@ latent_combine_kernel(const float* __restrict__ part, const T* __restrict__ gate
 // one sequence and walks the sequence's cache rows in tiles of 64 keys, which arrive by 16-byte
 // asynchronous copies straight from the pages into one of two stages of shared memory (keys past the
 // end are filled with zeros).  Per tile: warp w makes the scores of the tile's keys 8w .. 8w + 7 for all M
-// rows (mma.sync m16n8k16, queries and keys by ldmatrix, float accumulation over the whole cache row);
+// rows (mma.sync m16n8k16, queries and keys by ldmatrix, float accumulation over the whole cache row; with two
+// row tiles the block has sixteen warps and a pair of warps shares a group of keys, one row tile each);
 // maxima and sums of a row are exchanged through shared memory, the weights go there as bfloat16; then
 // every warp adds  P [M x 64] . C [64 x its NT * 8 columns of the latent]  to its float accumulators, the
 // latent read from the same stage by ldmatrix.trans.  Queries are scaled, rounded to bfloat16 and kept in
 // shared memory for the whole walk.  Splits, sink and gate are those of the kernel above.
 // ---------------------------------------------------------------------------------------------
-constexpr int kMmaWarps = 8;
+constexpr int kMmaKeyGroups = 8;   // groups of 8 keys in a tile: one per warp, or per pair of warps
 constexpr int kMmaKeys = 64;
 constexpr int kMmaPStride = kMmaKeys + 8;
 
@@ -302,8 +303,8 @@ __device__ __forceinline__ void copy16(void* dst, const void* src, bool real) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
 }
 
-template <int MT, int NT>
-__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+template <int MT, int NT, int W>
+__global__ void __launch_bounds__(W * 32, 1)
 latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16* __restrict__ pages,
                             const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
                             const int* __restrict__ positions, const __nv_bfloat16* __restrict__ gate, int gate_ld,
@@ -317,8 +318,8 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
   __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [M][DkP]
   __nv_bfloat16* Ks = Qs + M * DkP;                                      // [2][64][DkP]
   __nv_bfloat16* Ps = Ks + 2 * kMmaKeys * DkP;                           // [M][72]
-  float* red_max = reinterpret_cast<float*>(Ps + M * kMmaPStride);       // [warps][M]
-  float* red_sum = red_max + kMmaWarps * M;                              // [warps][M]
+  float* red_max = reinterpret_cast<float*>(Ps + M * kMmaPStride);       // [key groups][M]
+  float* red_sum = red_max + kMmaKeyGroups * M;                          // [key groups][M]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
 
   // which sequence, which of its row tiles
@@ -337,6 +338,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
   const int begin = n_splits > 1 ? split * split_keys : 0;
   const int end = n_splits > 1 ? min(pos_max + 1, begin + split_keys) : pos_max + 1;
   const int* bt = block_tables + (size_t)s * max_pages;
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
   // queries: scaled, rounded, zero beyond the valid rows and beyond Dk
   const float* q_rows = q_lat + ((size_t)tok0 * H + r0) * Dk;
@@ -370,16 +372,22 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
 #pragma unroll
       for (int i = 0; i < 4; ++i) o[mt][nt][i] = 0.f;
 
+  // A tile's rows are shared out by warp (rows warp, warp + 8, ...), a row's 16-byte pieces by lane: one page
+  // lookup per row and no division per piece.
   const int chunks_per_row = Dk / 8;
   auto load_tile = [&](int k0, int stage) {
     __nv_bfloat16* dst = Ks + stage * kMmaKeys * DkP;
-    for (int idx = threadIdx.x; idx < kMmaKeys * chunks_per_row; idx += blockDim.x) {
-      const int r = idx / chunks_per_row, c = (idx % chunks_per_row) * 8;
+#pragma unroll 2
+    for (int r = warp; r < kMmaKeys; r += W) {
       const int k = k0 + r;
       const bool real = k < end;
       const __nv_bfloat16* src = pages;
-      if (real) src = pages + ((size_t)bt[k / page_size] * page_size + k % page_size) * Dk + c;
-      copy16(dst + r * DkP + c, src, real);
+      if (real) {
+        const int page = page_shift >= 0 ? k >> page_shift : k / page_size;       // (pages of a power of two: no division)
+        src = pages + ((size_t)bt[page] * page_size + (k - page * page_size)) * Dk;
+      }
+      __nv_bfloat16* drow = dst + r * DkP;
+      for (int c = lane; c < chunks_per_row; c += 32) copy16(drow + 8 * c, real ? src + 8 * c : src, real);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
@@ -397,40 +405,58 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
     __syncthreads();
     const __nv_bfloat16* Kt = Ks + stage * kMmaKeys * DkP;
 
-    // scores of keys 8 * warp .. + 7 for all rows
-    float sc[MT][4];
+    // Scores of one group of 8 keys.  With 8 warps a warp takes its group for all row tiles; with 16 (two row
+    // tiles) warps 2 kg and 2 kg + 1 take group kg for one row tile each.  The sum over the row's entries runs in
+    // four chains (k-steps 0, 1, 2, 3 mod 4), so that a product does not wait for the one before it.
+    constexpr int QM = W == 16 ? 1 : MT;                      // row tiles a warp makes scores for
+    const int mt0 = W == 16 ? (warp & 1) : 0, kg = W == 16 ? (warp >> 1) : warp;
+    float ch[QM][4][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int q = 0; q < QM; ++q)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) sc[mt][i] = 0.f;
-    for (int kk = 0; kk < D16; kk += 32) {
-      uint32_t b[4];
-      ldsm4(b, Kt + (8 * warp + (lane & 7)) * DkP + kk + 8 * (lane >> 3));
-      const bool second = kk + 16 < D16;
+      for (int c = 0; c < 4; ++c)
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        uint32_t a[4];
-        const __nv_bfloat16* qa = Qs + (16 * mt + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + kk + 8 * (lane >> 4);
-        ldsm4(a, qa);
-        mma16816(sc[mt], a, b[0], b[1]);
-        if (second) {
-          ldsm4(a, qa + 16);
-          mma16816(sc[mt], a, b[2], b[3]);
+        for (int i = 0; i < 4; ++i) ch[q][c][i] = 0.f;
+    const __nv_bfloat16* kb = Kt + (8 * kg + (lane & 7)) * DkP + 8 * (lane >> 3);
+    const __nv_bfloat16* qb = Qs + (16 * mt0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + 8 * (lane >> 4);
+    for (int kk = 0; kk < D16; kk += 64) {
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int k32 = kk + 32 * half;
+        if (k32 < D16) {
+          uint32_t b[4];
+          ldsm4(b, kb + k32);
+          const bool second = k32 + 16 < D16;
+#pragma unroll
+          for (int q = 0; q < QM; ++q) {
+            uint32_t a[4];
+            ldsm4(a, qb + 16 * q * DkP + k32);
+            mma16816(ch[q][2 * half], a, b[0], b[1]);
+            if (second) {
+              ldsm4(a, qb + 16 * q * DkP + k32 + 16);
+              mma16816(ch[q][2 * half + 1], a, b[2], b[3]);
+            }
+          }
         }
       }
     }
-    const int key0 = k0 + 8 * warp + 2 * tq;
+    float sc[QM][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int q = 0; q < QM; ++q)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[q][i] = (ch[q][0][i] + ch[q][1][i]) + (ch[q][2][i] + ch[q][3][i]);
+    const int key0 = k0 + 8 * kg + 2 * tq;
+#pragma unroll
+    for (int q = 0; q < QM; ++q)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const int lim = min(pos_r[mt][j], end - 1);
-        if (key0 > lim) sc[mt][2 * j] = -INFINITY;
-        if (key0 + 1 > lim) sc[mt][2 * j + 1] = -INFINITY;
-        float mx = fmaxf(sc[mt][2 * j], sc[mt][2 * j + 1]);
+        const int lim = min(W == 16 ? (mt0 ? pos_r[MT - 1][j] : pos_r[0][j]) : pos_r[q][j], end - 1);
+        if (key0 > lim) sc[q][2 * j] = -INFINITY;
+        if (key0 + 1 > lim) sc[q][2 * j + 1] = -INFINITY;
+        float mx = fmaxf(sc[q][2 * j], sc[q][2 * j + 1]);
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        if (tq == 0) red_max[warp * M + 16 * mt + g + 8 * j] = mx;
+        if (tq == 0) red_max[kg * M + 16 * (mt0 + q) + g + 8 * j] = mx;
       }
     __syncthreads();
     float alpha[MT][2];
@@ -441,17 +467,25 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
         const int r = 16 * mt + g + 8 * j;
         float top = m_r[mt][j];
 #pragma unroll
-        for (int w = 0; w < kMmaWarps; ++w) top = fmaxf(top, red_max[w * M + r]);
+        for (int w = 0; w < kMmaKeyGroups; ++w) top = fmaxf(top, red_max[w * M + r]);
         const bool none = top == -INFINITY;
         alpha[mt][j] = (none || m_r[mt][j] == -INFINITY) ? (none ? 1.f : 0.f) : __expf(m_r[mt][j] - top);
-        const float p0 = (none || sc[mt][2 * j] == -INFINITY) ? 0.f : __expf(sc[mt][2 * j] - top);
-        const float p1 = (none || sc[mt][2 * j + 1] == -INFINITY) ? 0.f : __expf(sc[mt][2 * j + 1] - top);
-        *reinterpret_cast<__nv_bfloat162*>(Ps + r * kMmaPStride + 8 * warp + 2 * tq) = __floats2bfloat162_rn(p0, p1);
+        m_r[mt][j] = top;
+      }
+#pragma unroll
+    for (int q = 0; q < QM; ++q)
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int r = 16 * (mt0 + q) + g + 8 * j;
+        const float top = W == 16 ? (mt0 ? m_r[MT - 1][j] : m_r[0][j]) : m_r[q][j];
+        const bool none = top == -INFINITY;
+        const float p0 = (none || sc[q][2 * j] == -INFINITY) ? 0.f : __expf(sc[q][2 * j] - top);
+        const float p1 = (none || sc[q][2 * j + 1] == -INFINITY) ? 0.f : __expf(sc[q][2 * j + 1] - top);
+        *reinterpret_cast<__nv_bfloat162*>(Ps + r * kMmaPStride + 8 * kg + 2 * tq) = __floats2bfloat162_rn(p0, p1);
         float ps = p0 + p1;
         ps += __shfl_xor_sync(0xffffffffu, ps, 1);
         ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-        if (tq == 0) red_sum[warp * M + r] = ps;
-        m_r[mt][j] = top;
+        if (tq == 0) red_sum[kg * M + r] = ps;
       }
     __syncthreads();
 #pragma unroll
@@ -461,7 +495,7 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
         const int r = 16 * mt + g + 8 * j;
         float sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < kMmaWarps; ++w) sum += red_sum[w * M + r];
+        for (int w = 0; w < kMmaKeyGroups; ++w) sum += red_sum[w * M + r];
         l_r[mt][j] = l_r[mt][j] * alpha[mt][j] + sum;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -605,22 +639,23 @@ ERB_EXPORT int erb_latent_attention_mma(const float* q_lat, const void* pages, c
     return fail(ERB_ERR_UNSUPPORTED, "latent_attention_mma: sizes (latent %d, row %d) or alignment not supported", R, Dk);
   const int D16 = (Dk + 15) & ~15, DkP = D16 + 8, M = 16 * mt;
   const size_t smem = sizeof(__nv_bfloat16) * ((size_t)M * DkP + 2 * kMmaKeys * DkP + M * kMmaPStride) +
-                      sizeof(float) * 2 * kMmaWarps * M;
+                      sizeof(float) * 2 * kMmaKeyGroups * M;
   if (smem > 227 * 1024) return fail(ERB_ERR_UNSUPPORTED, "latent_attention_mma: rows of %d entries need %zu bytes", Dk, smem);
-  const int nt = (R / 8 + kMmaWarps - 1) / kMmaWarps;
+  const int warps = mt == 2 ? 16 : 8;            // two row tiles: sixteen warps, two per group of keys
+  const int nt = (R / 8 + warps - 1) / warps;
   const dim3 grid(n_tiles, n_splits);
   cudaStream_t st = (cudaStream_t)stream;
-#define ERB_LAT_MMA(MT_, NT_)                                                                                             \
+#define ERB_LAT_MMA(MT_, NT_, W_)                                                                                         \
   do {                                                                                                                    \
-    auto kern = latent_attention_mma_kernel<MT_, NT_>;                                                                    \
+    auto kern = latent_attention_mma_kernel<MT_, NT_, W_>;                                                                \
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                   \
     if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "latent_attention_mma: %s", cudaGetErrorString(e));                   \
-    launch_chained(kern, grid, dim3(kMmaWarps * 32), smem, st, q_lat, (const __nv_bfloat16*)pages, block_tables, max_pages, \
+    launch_chained(kern, grid, dim3(W_ * 32), smem, st, q_lat, (const __nv_bfloat16*)pages, block_tables, max_pages,      \
                    seq_starts, positions, (const __nv_bfloat16*)gate, gate_ld, sink, (__nv_bfloat16*)out, part, first_token, \
                    seq0, n_seqs, H, R, Dk, page_size, split_keys, n_splits, scale);                                       \
   } while (0)
-  if (mt == 1) { if (nt <= 2) ERB_LAT_MMA(1, 2); else if (nt <= 4) ERB_LAT_MMA(1, 4); else ERB_LAT_MMA(1, 8); }
-  else { if (nt <= 2) ERB_LAT_MMA(2, 2); else if (nt <= 4) ERB_LAT_MMA(2, 4); else ERB_LAT_MMA(2, 8); }
+  if (mt == 1) { if (nt <= 2) ERB_LAT_MMA(1, 2, 8); else if (nt <= 4) ERB_LAT_MMA(1, 4, 8); else ERB_LAT_MMA(1, 8, 8); }
+  else { if (nt <= 2) ERB_LAT_MMA(2, 2, 16); else ERB_LAT_MMA(2, 4, 16); }
 #undef ERB_LAT_MMA
   return check_launch("latent_attention_mma");
 #else
