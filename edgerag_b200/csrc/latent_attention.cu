@@ -605,7 +605,7 @@ ERB_EXPORT int erb_latent_attention(const float* q_lat, const void* pages, const
   if (H <= 0 || R <= 0 || R % 2 || dr % 2 || page_size <= 0 || n_splits < 1 || n_splits > kCombineSplits ||
       (n_splits > 1 && (!part || split_keys <= 0)))
     return fail(ERB_ERR_ARG, "latent_attention: bad sizes (latent and rotated widths must be even, at most %d splits)", kCombineSplits);
-  if (Dk > 640) return fail(ERB_ERR_UNSUPPORTED, "latent_attention: cache rows of %d entries (at most 640)", Dk);
+  if (Dk > 1024) return fail(ERB_ERR_UNSUPPORTED, "latent_attention: cache rows of %d entries (at most 1024)", Dk);
   const int n_rows = n_tokens * H;
   const dim3 grid((n_rows + kLatWarps - 1) / kLatWarps, n_splits);
   cudaStream_t st = (cudaStream_t)stream;
@@ -614,7 +614,8 @@ ERB_EXPORT int erb_latent_attention(const float* q_lat, const void* pages, const
   if (Dk <= 128) ERB_LAT(2);
   else if (Dk <= 256) ERB_LAT(4);
   else if (Dk <= 384) ERB_LAT(6);
-  else ERB_LAT(10);
+  else if (Dk <= 640) ERB_LAT(10);
+  else ERB_LAT(16);
 #undef ERB_LAT
   int rc = check_launch("latent_attention");
   if (rc || n_splits == 1) return rc;
