@@ -342,6 +342,9 @@ struct RopeArgs {
   __nv_bfloat16* k_pages;      // [page][kv head][offset][head_dim]
   __nv_bfloat16* v_pages;
   int nq, nkv, head_dim, page_size;
+  // MODE 2 only: g * sigmoid(alpha g) * (u + shift) with g = min(g, limit), u = clamp(u, -limit, limit) when limit > 0;
+  // the defaults are the SwiGLU gate
+  float glu_limit = 0.f, glu_alpha = 1.f, glu_shift = 0.f;
 };
 
 // NT: tiles of 8 rows of `a`; RT: tiles of 16 rows of w per block; kSkWarps: warps per block;
@@ -456,7 +459,17 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
       v1 = __bfloat162float(__float2bfloat16_rn(v1));
       if constexpr (GLU) {
         const int n = n0 + rr;
-        if (n < N) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(silu_mul(v0, v1));
+        float act;
+        if (ra.glu_limit > 0.f || ra.glu_alpha != 1.f || ra.glu_shift != 0.f) {     // the bounded gate, as its own kernel writes it
+          if (ra.glu_limit > 0.f) {
+            v0 = fminf(v0, ra.glu_limit);
+            v1 = fminf(fmaxf(v1, -ra.glu_limit), ra.glu_limit);
+          }
+          act = v0 / (1.f + expf(-ra.glu_alpha * v0)) * (v1 + ra.glu_shift);
+        } else {
+          act = silu_mul(v0, v1);
+        }
+        if (n < N) reinterpret_cast<__nv_bfloat16*>(out)[(size_t)m * ldo + n] = __float2bfloat16_rn(act);
       } else {
         const int D = ra.head_dim, half = D / 2;
         const int slot = ra.slots[m];
@@ -672,5 +685,18 @@ ERB_EXPORT int erb_linear_skinny_glu(const void* a, const void* w, void* out, in
   if (rc) return rc;
   return launch_skinny_mode<2>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, M, N, K, lda, ldw, ldo,
                                (cudaStream_t)stream);
+}
+
+// The same with the bounded gate of `glu_bounded_kernel` (elementwise.cu) in the epilogue:
+// out = g * sigmoid(alpha g) * (u + shift), g = min(g, limit), u = clamp(u, -limit, limit) for limit > 0.
+ERB_EXPORT int erb_linear_skinny_glu_bounded(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw,
+                                             int ldo, float limit, float alpha, float shift, void* stream) {
+  if (M <= 0) return ERB_OK;
+  int rc = check_skinny("linear_skinny_glu_bounded", a, w, M, N, K, lda, ldw, ldo);
+  if (rc) return rc;
+  RopeArgs ra{};
+  ra.glu_limit = limit; ra.glu_alpha = alpha; ra.glu_shift = shift;
+  return launch_skinny_mode<2>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, M, N, K, lda, ldw, ldo,
+                               (cudaStream_t)stream, ra);
 }
 #endif  // ERB_ELEM == 1

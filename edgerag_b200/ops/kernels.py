@@ -37,6 +37,8 @@ _SIGNATURES = {
                    c_void_p, c_longlong, c_void_p],
     "erb_linear_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_skinny_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "erb_linear_skinny_glu_bounded": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                      c_float, c_void_p],
     "erb_linear_skinny_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_linear_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -470,10 +472,11 @@ def linear_glu_supported(a: torch.Tensor, weight: torch.Tensor, max_rows: int = 
     return a.shape[0] <= max_rows and weight.shape[0] % 2 == 0 and linear_few_rows_supported(a, weight, lda)
 
 
-def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bounded: tuple[float, float, float] | None = None) -> None:
     """out[M, N] = silu(a @ gate^T) * (a @ up^T) for ``weight = [gate; up]`` of shape [2N, K], in one
     launch; equal to ``linear`` into an [M, 2N] buffer followed by ``swiglu`` (each product is rounded
-    to bfloat16 before the gate)."""
+    to bfloat16 before the gate).  ``bounded = (limit, alpha, shift)``: the gate of ``glu_bounded`` instead,
+    equal to ``linear`` followed by ``glu_bounded``."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
     _need(out, "out", torch.bfloat16, contiguous=False)
     m, k = a.shape
@@ -482,6 +485,11 @@ def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None
         raise KernelError("linear_glu: shapes, strides or operands not supported")
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
+    if bounded is not None:
+        limit, alpha, shift = bounded
+        _call(_fn("gemm", "bfloat16", "erb_linear_skinny_glu_bounded"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
+              lda, k, ldo, float(limit), float(alpha), float(shift), _stream())
+        return
     _call(_fn("gemm", "bfloat16", "erb_linear_skinny_glu"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
           lda, k, ldo, _stream())
 

@@ -4,7 +4,8 @@
 
 ``alpha``, ``shift`` and ``limit`` are constructor arguments (``limit <= 0``: unbounded; ``alpha = 1, shift = 0``
 is the SwiGLU gate), as are the tensors' names.  ``gate`` and ``up`` are stored as one matrix so that one
-product feeds the activation kernel, which works in float and rounds once.
+product feeds the activation kernel, which works in float and rounds once; for the few rows of a decode step
+the product and the gate are one kernel with the same result.
 """
 
 from __future__ import annotations
@@ -41,10 +42,14 @@ class BoundedGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = x.shape[0]
-        gate_up = ctx.buf("ffn.gate_up", (n, 2 * self.intermediate), self.dtype)
-        kernels.linear(x, self.w_gate_up, gate_up)
         act = ctx.buf("ffn.act", (n, self.intermediate), self.dtype)
-        kernels.glu_bounded(gate_up, act, self.limit, self.alpha, self.shift)
+        if kernels.linear_glu_supported(x, self.w_gate_up):
+            # a few rows: product and gate in one kernel, the same bits as the two kernels below
+            kernels.linear_glu(x, self.w_gate_up, act, bounded=(self.limit, self.alpha, self.shift))
+        else:
+            gate_up = ctx.buf("ffn.gate_up", (n, 2 * self.intermediate), self.dtype)
+            kernels.linear(x, self.w_gate_up, gate_up)
+            kernels.glu_bounded(gate_up, act, self.limit, self.alpha, self.shift)
         y = ctx.buf("ffn.out", (n, self.hidden), self.dtype)
         kernels.linear(act, self.w_down, y)
         return y

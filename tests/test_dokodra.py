@@ -522,6 +522,26 @@ def test_bounded_gate_softcap_and_offset_norm_kernels(dtype):
     assert torch.allclose(normed.double().cpu(), want, atol=1e-5 if dtype == torch.float32 else 2e-2, rtol=tol)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("rows", [1, 5, 16])
+def test_bounded_gate_in_the_product_equals_the_two_kernels(rows):
+    """The few-rows product with the bounded gate in its epilogue gives the bits of the product followed by the gate kernel."""
+    from edgerag_b200.ops import kernels
+
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(rows, 96, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(2 * 72, 96, generator=g) * 0.3).to(torch.bfloat16).cuda()
+    assert kernels.linear_glu_supported(x, w)
+    fused = torch.zeros(rows, 72, dtype=torch.bfloat16).cuda()
+    kernels.linear_glu(x, w, fused, bounded=(0.8, 1.702, 1.0))
+    gate_up = torch.zeros(rows, 144, dtype=torch.bfloat16).cuda()
+    kernels.linear(x, w, gate_up)
+    two = torch.zeros(rows, 72, dtype=torch.bfloat16).cuda()
+    kernels.glu_bounded(gate_up, two, 0.8, 1.702, 1.0)
+    assert torch.equal(fused, two)
+    assert (gate_up[:, :72].float() > 0.8).any()
+
+
 # --- generation through the engine's own entry point -----------------------------------------------
 
 def plain_greedy(raw, tensors, prompt, n_new):
