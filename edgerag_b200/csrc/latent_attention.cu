@@ -273,7 +273,9 @@ latent_combine_kernel(const float* __restrict__ part, const T* __restrict__ gate
 // end are filled with zeros).  Per tile: warp w makes the scores of the tile's keys 8w .. 8w + 7 for all M
 // rows (mma.sync m16n8k16, queries and keys by ldmatrix, float accumulation over the whole cache row; with two
 // row tiles the block has sixteen warps and a pair of warps shares a group of keys, one row tile each);
-// maxima and sums of a row are exchanged through shared memory, the weights go there as bfloat16; then
+// the groups' maxima and sums of a row go through shared memory to the one thread that keeps the row's
+// running maximum and denominator and hands back the new maximum and the rescaling factor; the weights go
+// to shared memory as bfloat16; then
 // every warp adds  P [M x 64] . C [64 x its NT * 8 columns of the latent]  to its float accumulators, the
 // latent read from the same stage by ldmatrix.trans.  Queries are scaled, rounded to bfloat16 and kept in
 // shared memory for the whole walk.  Splits, sink and gate are those of the kernel above.
@@ -290,6 +292,10 @@ __device__ __forceinline__ void ldsm4(uint32_t* r, const void* p) {
 __device__ __forceinline__ void ldsm4t(uint32_t* r, const void* p) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm4s(uint32_t* r, uint32_t a) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 __device__ __forceinline__ void mma16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
@@ -320,6 +326,8 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
   __nv_bfloat16* Ps = Ks + 2 * kMmaKeys * DkP;                           // [M][72]
   float* red_max = reinterpret_cast<float*>(Ps + M * kMmaPStride);       // [key groups][M]
   float* red_sum = red_max + kMmaKeyGroups * M;                          // [key groups][M]
+  float* row_top = red_sum + kMmaKeyGroups * M;                          // [M]: a row's maximum so far (at the end: its final one)
+  float* row_alpha = row_top + M;                                        // [M]: what the tile rescales the row by (at the end: its sum)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tq = lane & 3;
 
   // which sequence, which of its row tiles
@@ -354,16 +362,16 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
   }
 
   int pos_r[MT][2];
-  float m_r[MT][2], l_r[MT][2];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int r = 16 * mt + g + 8 * j;
       pos_r[mt][j] = r < valid ? positions[tok0 + (r0 + r) / H] : -1;
-      m_r[mt][j] = -INFINITY;
-      l_r[mt][j] = 0.f;
     }
+  // Row r's running maximum and denominator are kept by thread r alone (the first M threads of the block), which
+  // also tells the others, per tile, the new maximum and the factor that rescales what has been summed so far.
+  float m_own = -INFINITY, l_own = 0.f, alpha_own = 1.f;
   float o[MT][NT][4];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
@@ -417,23 +425,25 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
       for (int c = 0; c < 4; ++c)
 #pragma unroll
         for (int i = 0; i < 4; ++i) ch[q][c][i] = 0.f;
-    const __nv_bfloat16* kb = Kt + (8 * kg + (lane & 7)) * DkP + 8 * (lane >> 3);
-    const __nv_bfloat16* qb = Qs + (16 * mt0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + 8 * (lane >> 4);
+    const uint32_t kb = (uint32_t)__cvta_generic_to_shared(Kt + (8 * kg + (lane & 7)) * DkP + 8 * (lane >> 3));
+    const uint32_t qb = (uint32_t)__cvta_generic_to_shared(Qs + (16 * mt0 + (lane & 7) + 8 * ((lane >> 3) & 1)) * DkP + 8 * (lane >> 4));
+    const uint32_t q_tile = 16 * DkP * (uint32_t)sizeof(__nv_bfloat16);
+#pragma unroll 2
     for (int kk = 0; kk < D16; kk += 64) {
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int k32 = kk + 32 * half;
         if (k32 < D16) {
           uint32_t b[4];
-          ldsm4(b, kb + k32);
+          ldsm4s(b, kb + 2 * k32);
           const bool second = k32 + 16 < D16;
 #pragma unroll
           for (int q = 0; q < QM; ++q) {
             uint32_t a[4];
-            ldsm4(a, qb + 16 * q * DkP + k32);
+            ldsm4s(a, qb + q * q_tile + 2 * k32);
             mma16816(ch[q][2 * half], a, b[0], b[1]);
             if (second) {
-              ldsm4(a, qb + 16 * q * DkP + k32 + 16);
+              ldsm4s(a, qb + q * q_tile + 2 * k32 + 32);
               mma16816(ch[q][2 * half + 1], a, b[2], b[3]);
             }
           }
@@ -459,25 +469,23 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
         if (tq == 0) red_max[kg * M + 16 * (mt0 + q) + g + 8 * j] = mx;
       }
     __syncthreads();
-    float alpha[MT][2];
+    if ((int)threadIdx.x < M) {
+      const int r = threadIdx.x;
+      float top = m_own;
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int r = 16 * mt + g + 8 * j;
-        float top = m_r[mt][j];
-#pragma unroll
-        for (int w = 0; w < kMmaKeyGroups; ++w) top = fmaxf(top, red_max[w * M + r]);
-        const bool none = top == -INFINITY;
-        alpha[mt][j] = (none || m_r[mt][j] == -INFINITY) ? (none ? 1.f : 0.f) : __expf(m_r[mt][j] - top);
-        m_r[mt][j] = top;
-      }
+      for (int w = 0; w < kMmaKeyGroups; ++w) top = fmaxf(top, red_max[w * M + r]);
+      alpha_own = (top == -INFINITY) ? 1.f : (m_own == -INFINITY ? 0.f : __expf(m_own - top));
+      m_own = top;
+      row_top[r] = top;
+      row_alpha[r] = alpha_own;
+    }
+    __syncthreads();
 #pragma unroll
     for (int q = 0; q < QM; ++q)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int r = 16 * (mt0 + q) + g + 8 * j;
-        const float top = W == 16 ? (mt0 ? m_r[MT - 1][j] : m_r[0][j]) : m_r[q][j];
+        const float top = row_top[r];
         const bool none = top == -INFINITY;
         const float p0 = (none || sc[q][2 * j] == -INFINITY) ? 0.f : __expf(sc[q][2 * j] - top);
         const float p1 = (none || sc[q][2 * j + 1] == -INFINITY) ? 0.f : __expf(sc[q][2 * j + 1] - top);
@@ -487,22 +495,24 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
         ps += __shfl_xor_sync(0xffffffffu, ps, 2);
         if (tq == 0) red_sum[kg * M + r] = ps;
       }
-    __syncthreads();
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
-        const int r = 16 * mt + g + 8 * j;
-        float sum = 0.f;
-#pragma unroll
-        for (int w = 0; w < kMmaKeyGroups; ++w) sum += red_sum[w * M + r];
-        l_r[mt][j] = l_r[mt][j] * alpha[mt][j] + sum;
+        const float alpha = row_alpha[16 * mt + g + 8 * j];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          o[mt][nt][2 * j] *= alpha[mt][j];
-          o[mt][nt][2 * j + 1] *= alpha[mt][j];
+          o[mt][nt][2 * j] *= alpha;
+          o[mt][nt][2 * j + 1] *= alpha;
         }
       }
+    __syncthreads();
+    if ((int)threadIdx.x < M) {
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kMmaKeyGroups; ++w) sum += red_sum[w * M + threadIdx.x];
+      l_own = l_own * alpha_own + sum;
+    }
     // O += P . C for this warp's columns
 #pragma unroll
     for (int ks = 0; ks < kMmaKeys / 16; ++ks) {
@@ -527,6 +537,11 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
     __syncthreads();
   }
 
+  if ((int)threadIdx.x < M) {
+    row_top[threadIdx.x] = m_own;
+    row_alpha[threadIdx.x] = l_own;
+  }
+  __syncthreads();
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -534,16 +549,17 @@ latent_attention_mma_kernel(const float* __restrict__ q_lat, const __nv_bfloat16
       const int r = 16 * mt + g + 8 * j;
       if (r >= valid) continue;
       const int tok = tok0 + (r0 + r) / H, h = (r0 + r) % H;
+      const float m_fin = row_top[r], l_fin = row_alpha[r];
       if (n_splits > 1) {
         float* dst = part + ((size_t)((tok - first_token) * H + h) * n_splits + split) * (R + 2);
-        if (warp == 0 && tq == 0) { dst[0] = m_r[mt][j]; dst[1] = l_r[mt][j]; }
+        if (warp == 0 && tq == 0) { dst[0] = m_fin; dst[1] = l_fin; }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const int c = (warp * NT + nt) * 8 + 2 * tq;
           if (c < R) { dst[2 + c] = o[mt][nt][2 * j]; dst[3 + c] = o[mt][nt][2 * j + 1]; }
         }
       } else {
-        const float f = finish_factor(m_r[mt][j], l_r[mt][j], sink, h,
+        const float f = finish_factor(m_fin, l_fin, sink, h,
                                       gate ? __bfloat162float(gate[(size_t)tok * gate_ld + h]) : 0.f, gate != nullptr);
         __nv_bfloat16* dst = out + ((size_t)tok * H + h) * R;
 #pragma unroll
@@ -640,7 +656,7 @@ ERB_EXPORT int erb_latent_attention_mma(const float* q_lat, const void* pages, c
     return fail(ERB_ERR_UNSUPPORTED, "latent_attention_mma: sizes (latent %d, row %d) or alignment not supported", R, Dk);
   const int D16 = (Dk + 15) & ~15, DkP = D16 + 8, M = 16 * mt;
   const size_t smem = sizeof(__nv_bfloat16) * ((size_t)M * DkP + 2 * kMmaKeys * DkP + M * kMmaPStride) +
-                      sizeof(float) * 2 * kMmaKeyGroups * M;
+                      sizeof(float) * (2 * kMmaKeyGroups * M + 2 * M);
   if (smem > 227 * 1024) return fail(ERB_ERR_UNSUPPORTED, "latent_attention_mma: rows of %d entries need %zu bytes", Dk, smem);
   const int warps = mt == 2 ? 16 : 8;            // two row tiles: sixteen warps, two per group of keys
   const int nt = (R / 8 + warps - 1) / warps;

@@ -697,7 +697,7 @@ def latent_mma_supported(dtype: torch.dtype, rank: int, rot_dim: int) -> bool:
     of 64 rows beside 32 query rows within an SM's shared memory."""
     dk = rank + rot_dim
     d16 = -(-dk // 16) * 16 + 8
-    smem = 2 * (32 * d16 + 2 * 64 * d16 + 32 * 72) + 4 * 2 * 8 * 32
+    smem = 2 * (32 * d16 + 2 * 64 * d16 + 32 * 72) + 4 * (2 * 8 * 32 + 2 * 32)
     return dtype == torch.bfloat16 and rank % 8 == 0 and dk % 8 == 0 and 0 < rank <= 512 and smem <= 227 * 1024
 
 
