@@ -142,18 +142,17 @@ ssm_scan_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ p
     if (i < NL && n0 + i < N) s_glob[(size_t)(n0 + i) * P + p] = S[i];
 }
 
-// The same scan for states whose row count is a multiple of 16: a block owns PB (16 or 32) columns of one
-// head's state, thread (l, p) rows 16 l .. 16 l + 15 of column p, so a head gives P / PB blocks of N / 16 * PB
-// light threads (more blocks in flight, and a warp reads B and C as 16-byte broadcasts).  Same arithmetic in
-// the same order per state entry; the partial sums of a column are added in the order of l.
-template <typename T>
+// The same scan for states whose row count is a multiple of NL (8 or 16): a block owns PB (16 or 32) columns of
+// one head's state, thread (l, p) rows NL l .. NL l + NL - 1 of column p, so a head gives P / PB blocks of
+// N / NL * PB light threads (more warps in flight to hide the dependent steps of a token, and a warp reads B and C
+// as 16-byte broadcasts).  Same arithmetic per state entry; the partial sums of a column are added in the order of l.
+template <typename T, int NL>
 __global__ void __launch_bounds__(512)
 ssm_scan16_kernel(const T* __restrict__ xbc, int channels, const T* __restrict__ proj, int ld, int off_dt,
                   const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip,
                   float* __restrict__ state, const int* __restrict__ seq_starts, const int* __restrict__ state_slots,
                   float* __restrict__ y, int H, int P, int N, int G, int PB) {
   chain_wait();
-  constexpr int NL = 16;
   extern __shared__ __align__(16) float smem[];
   const int L = N / NL;
   float* b_s = smem;                                   // [chunk][N]
@@ -271,13 +270,18 @@ ERB_EXPORT int erb_ssm_scan(const void* xbc, int channels, const void* proj, int
   if (n_seqs <= 0) return ERB_OK;
   if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G || P > 512) return fail(ERB_ERR_ARG, "ssm_scan: bad sizes (columns of at most 512)");
   const int PB = P % 32 == 0 ? 32 : (P % 16 == 0 ? 16 : 0);
-  if (PB && N % 16 == 0 && (N / 16) * PB <= 512) {
-    const size_t smem16 = sizeof(float) * ((size_t)kScanChunk * (2 * N + PB + 2 + (size_t)(N / 16) * PB));
+  // rows per thread: 8 where that still gives a block of at most 512 threads, else 16 (a function of the sizes
+  // alone: the order in which a column's partial sums are added must not depend on the batch)
+  const int NLc = (N % 8 == 0 && (N / 8) * PB <= 512) ? 8 : 16;
+  if (PB && N % NLc == 0 && (N / NLc) * PB <= 512) {
+    const int L = N / NLc;
+    const size_t smem16 = sizeof(float) * ((size_t)kScanChunk * (2 * N + PB + 2 + (size_t)L * PB));
+    auto kern = NLc == 8 ? ssm_scan16_kernel<elem_t, 8> : ssm_scan16_kernel<elem_t, 16>;
     if (smem16 > 48 * 1024) {
-      cudaError_t e = cudaFuncSetAttribute(ssm_scan16_kernel<elem_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem16);
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem16);
       if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "ssm_scan: %s", cudaGetErrorString(e));
     }
-    launch_chained(ssm_scan16_kernel<elem_t>, dim3(H, n_seqs, P / PB), dim3((N / 16) * PB), smem16, (cudaStream_t)stream,
+    launch_chained(kern, dim3(H, n_seqs, P / PB), dim3(L * PB), smem16, (cudaStream_t)stream,
                    (const elem_t*)xbc, channels, (const elem_t*)proj, ld, off_dt, dt_bias, a_log, d_skip, state, seq_starts,
                    state_slots, y, H, P, N, G, PB);
     return check_launch("ssm_scan");
