@@ -102,8 +102,10 @@ def main(argv: list[str] | None = None) -> int:
             arch = architecture_of(raw)
             plan = arch.make_plan(arch.read_config(raw, args.config))
             specs = DecoderModel(plan, torch.float32, torch.device("cpu")).weight_specs()
+            # tensors get the prefix a checkpoint of the architecture carries ("model." where the plan knows it)
+            prefix = "model." if "model." in plan.name_prefixes else plan.name_prefixes[0]
             write_model_folder(args.save_model, raw, specs, args.random_weights, std=args.weights_std,
-                               dtype=resolve_dtype(args.dtype))
+                               dtype=resolve_dtype(args.dtype), name_prefix=prefix)
             engine = Engine.from_pretrained(args.save_model, options)
         else:
             engine = Engine.from_config(raw, args.random_weights, args.weights_std, options)

@@ -602,3 +602,20 @@ def test_trace_replay_program(folders, tmp_path):
     assert_close(got[0], wa[[0, 29]], "float32", "step 0")
     assert_close(got[1], torch.stack([wa[30], wb[7]]), "float32", "step 1")
     assert_close(got[2], torch.stack([wb[8], wa[39]]), "float32", "step 2")
+
+
+@pytest.mark.gpu
+def test_command_line_with_random_weights(tmp_path):
+    """``python -m edgerag_b200`` on a Dokodra configuration: seeded random weights written as a model folder, the
+    folder loaded again, a few greedy tokens for two prompts; the same tokens when the folder is given as --model."""
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(FULL))
+    base = [sys.executable, "-m", "edgerag_b200", "--dtype", "fp32", "--num-blocks", "16", "--max-batch-size", "2", "--chunk-size", "16",
+            "--max-new-tokens", "5", "--prompt-ids", "3,1,4,1,5,9,2,6", "--prompt-ids", "7", "--json"]
+    first = subprocess.run(base + ["--random-weights", "3", "--config", str(cfg), "--save-model", str(tmp_path / "m"), "--weights-std", "0.1"],
+                           capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert first.returncode == 0, first.stderr[-2000:]
+    again = subprocess.run(base + ["--model", str(tmp_path / "m")], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert again.returncode == 0, again.stderr[-2000:]
+    a, b = (json.loads(p.stdout.strip().splitlines()[-1])["outputs"] for p in (first, again))
+    assert [len(o["token_ids"]) for o in a] == [5, 5] and a == b
