@@ -266,13 +266,14 @@ ERB_EXPORT int erb_conv_state_update(const void* proj, int n_seqs, int ld, int o
 
 ERB_EXPORT int erb_ssm_scan(const void* xbc, int channels, const void* proj, int ld, int off_dt, const float* dt_bias,
                             const float* a_log, const float* d_skip, float* state, const int* seq_starts,
-                            const int* state_slots, float* y, int n_seqs, int H, int P, int N, int G, void* stream) {
+                            const int* state_slots, float* y, int n_seqs, int n_tokens, int H, int P, int N, int G, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
   if (H <= 0 || P <= 0 || N <= 0 || G <= 0 || H % G || P > 512) return fail(ERB_ERR_ARG, "ssm_scan: bad sizes (columns of at most 512)");
   const int PB = P % 32 == 0 ? 32 : (P % 16 == 0 ? 16 : 0);
-  // rows per thread: 8 where that still gives a block of at most 512 threads, else 16 (a function of the sizes
-  // alone: the order in which a column's partial sums are added must not depend on the batch)
-  const int NLc = (N % 8 == 0 && (N / 8) * PB <= 512) ? 8 : 16;
+  // rows per thread: 16 for a step of single tokens (fewer, busier threads: the step is the state's read and write),
+  // 8 where portions are walked and that still gives a block of at most 512 threads (twice the warps to hide a token's
+  // dependent steps).  The two differ in the order in which a column's partial sums are added, that is by rounding.
+  const int NLc = (n_tokens > n_seqs && N % 8 == 0 && (N / 8) * PB <= 512) ? 8 : 16;
   if (PB && N % NLc == 0 && (N / NLc) * PB <= 512) {
     const int L = N / NLc;
     const size_t smem16 = sizeof(float) * ((size_t)kScanChunk * (2 * N + PB + 2 + (size_t)L * PB));

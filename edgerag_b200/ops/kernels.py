@@ -85,7 +85,7 @@ _SIGNATURES = {
                       c_void_p, c_void_p, c_void_p],
     "erb_conv_state_update": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
     "erb_ssm_scan": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                     c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_gated_group_norm": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_float, c_void_p],
     "erb_sample_rows": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -796,7 +796,7 @@ def ssm_scan(xbc: torch.Tensor, proj: torch.Tensor, off_dt: int, dt_bias: torch.
         raise KernelError("ssm_scan: shapes disagree")
     _call(_fn("ssm", _elem(xbc), "erb_ssm_scan"), xbc.data_ptr(), xbc.shape[1], proj.data_ptr(),
           proj.stride(0) if n > 1 else proj.shape[1], int(off_dt), dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(),
-          state.data_ptr(), seq_starts.data_ptr(), state_slots.data_ptr(), y.data_ptr(), int(n_seqs), heads, p, n_state,
+          state.data_ptr(), seq_starts.data_ptr(), state_slots.data_ptr(), y.data_ptr(), int(n_seqs), n, heads, p, n_state,
           int(n_groups), _stream())
 
 
