@@ -12,7 +12,8 @@ What the reference spreads over ``BlockTable`` (edgerag/cache/block_table.py:26-
   about length (edgerag/cache/block_table.py:60-79), and growth happens before the count advances,
   so a failed growth leaves the request untouched.
 * Pages go back to the pool when the request is released, or, in a windowed group, as soon as no
-  later query can see any key of the page.
+  later query can see any key of the page.  A windowed group may keep its first tokens visible for
+  good (``keep_first``): the pages that hold any of them are never given back early.
 * Beside the pages, every request holds one **state slot**: the index of a fixed-size record in
   each state tensor that a mixer registered (none for the Llama decoder).  Slots are zeroed when
   handed out.
@@ -43,6 +44,8 @@ class KVGroupSpec:
     #: width of a cached value row when it differs from the key's (a mixer that caches keys and
     #: values of different sizes, or a single latent per token with ``v_head_dim = 0``); None: head_dim
     v_head_dim: int | None = None
+    #: with a window: the first tokens of a sequence that stay visible whatever the distance
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -81,7 +84,8 @@ class BlockTable:
     """One request's pages in one group.  ``pages[i]`` is ``NO_PAGE`` once a window has passed page i."""
 
     pages: list[int] = field(default_factory=list)
-    first_live: int = 0  # index of the first page not yet given back
+    first_live: int = 0  # index of the first page not yet given back (pages before ``kept`` aside)
+    kept: int = 0        # leading pages that are never given back early (they hold tokens every query sees)
     #: the same ids as an int32 array (capacity grows by doubling), for building batches without Python loops
     _array: np.ndarray = field(default_factory=lambda: np.zeros(16, np.int32), repr=False, compare=False)
 
@@ -151,7 +155,7 @@ class CacheManager:
             full = self.pages_for(final_tokens)
             if g.window > 0:
                 span = g.window + max(1, max_step_tokens)
-                out.append(min(full, self.pages_for(span) + 1))
+                out.append(min(full, self.pages_for(span) + 1 + self.pages_for(g.keep_first)))
             else:
                 out.append(full)
         return out
@@ -161,7 +165,8 @@ class CacheManager:
 
     def held_pages(self, request_id: object) -> list[int]:
         rc = self.requests[request_id]
-        return [len(t.pages) - t.first_live for t in rc.tables]   # released pages are exactly the first ones
+        # released pages are exactly those from the kept ones up to the first live one
+        return [len(t.pages) - max(0, t.first_live - t.kept) for t in rc.tables]
 
     # --- life of a request ------------------------------------------------------------------------
 
@@ -223,6 +228,8 @@ class CacheManager:
             # A later query sits at position >= num_tokens and sees keys > position - window, so
             # keys <= num_tokens - window are dead; page i is dead when its last key is.
             dead_upto = rc.num_tokens - g.window
+            t.kept = min(self.pages_for(g.keep_first), len(t.pages))
+            t.first_live = max(t.first_live, t.kept)
             while t.first_live < len(t.pages) and (t.first_live + 1) * ps - 1 <= dead_upto:
                 page = t.pages[t.first_live]
                 self.pages[gi].free([page])

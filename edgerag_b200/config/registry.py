@@ -69,6 +69,9 @@ def _register_builtin() -> None:
     from ..models.dokodra import DokodraConfig, dokodra_plan
 
     register_architecture(["Dokodra", "dokodra"], DokodraConfig.from_dict, dokodra_plan)
+    from ..models.vokusun import VokusunConfig, vokusun_plan
+
+    register_architecture(["Vokusun", "vokusun"], VokusunConfig.from_dict, vokusun_plan)
 
 
 _register_builtin()

@@ -7,7 +7,8 @@
 // Cache layout (one layer): pages[page][kv head][offset][D]; a token at logical position p of a
 // sequence lives in page block_table[seq][p / page_size] at offset p % page_size.  Keys are
 // stored already rotated.  A query at position p sees keys max(0, p - window + 1) .. p
-// (window <= 0: all keys 0 .. p).  Query head h reads kv head h / (nq / nkv).
+// (window <= 0: all keys 0 .. p) and, with a window, also the keys 0 .. keep_first - 1 whatever their
+// distance.  Query head h reads kv head h / (nq / nkv).
 //
 // Both kernels give every thread its own keys and its own online-softmax state (running max,
 // denominator, float accumulator of D values), so the inner loop has no cross-thread traffic;
@@ -116,7 +117,7 @@ attention_rows_kernel(const T* __restrict__ q, int q_row_stride, const T* __rest
                       const T* __restrict__ v_pages, const int* __restrict__ block_tables, int max_pages,
                       const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                       T* __restrict__ out, int out_row_stride, int n_tokens, int nq, int nkv,
-                      int page_size, int window, float scale) {
+                      int page_size, int window, int keep_first, float scale) {
   chain_wait();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -136,6 +137,12 @@ attention_rows_kernel(const T* __restrict__ q, int q_row_stride, const T* __rest
 
   LaneState<D> st;
   st.init();
+  const int kept = min(keep_first, k_lo);     // the first keys that the window would hide
+  for (int k = lane; k < kept; k += 32) {
+    const int page = bt[k / page_size];
+    const size_t row = (((size_t)page * nkv + kvh) * page_size + (k % page_size)) * D;
+    st.template visit<T>(q_s, k_pages + row, v_pages + row, scale);
+  }
   for (int k = k_lo + lane; k <= pos; k += 32) {
     const int page = bt[k / page_size];
     const size_t row = (((size_t)page * nkv + kvh) * page_size + (k % page_size)) * D;
@@ -168,7 +175,7 @@ attention_decode_split_kernel(const T* __restrict__ q, int q_row_stride, const T
                               int max_pages, const int* __restrict__ token_of_seq,
                               const int* __restrict__ positions, float* __restrict__ part_acc,
                               float* __restrict__ part_ml, int max_splits, int nq, int nkv, int page_size,
-                              int window, int split_keys, float scale) {
+                              int window, int keep_first, int split_keys, float scale) {
   chain_wait();
   extern __shared__ float smem[];
   float* q_s = smem;                                   // D
@@ -184,6 +191,7 @@ attention_decode_split_kernel(const T* __restrict__ q, int q_row_stride, const T
   const int begin = max(k_lo, (first_split + split) * split_keys);
   const int end = min(pos + 1, (first_split + split + 1) * split_keys);
   if (begin >= end) return;  // this split does not exist for this sequence
+  const int kept = split == 0 ? min(keep_first, k_lo) : 0;   // the first split also takes the keys kept before the window
 
   const T* q_row = q + (size_t)t * q_row_stride + (size_t)h * D;
   for (int d = threadIdx.x; d < D; d += blockDim.x) q_s[d] = Elem<T>::load(q_row + d);
@@ -193,6 +201,11 @@ attention_decode_split_kernel(const T* __restrict__ q, int q_row_stride, const T
   const int* bt = block_tables + (size_t)seq * max_pages;
   LaneState<D> st;
   st.init();
+  for (int k = (int)threadIdx.x; k < kept; k += kDecodeWarps * 32) {
+    const int page = bt[k / page_size];
+    const size_t row = (((size_t)page * nkv + kvh) * page_size + (k % page_size)) * D;
+    st.template visit<T>(q_s, k_pages + row, v_pages + row, scale);
+  }
   for (int k = begin + (int)threadIdx.x; k < end; k += kDecodeWarps * 32) {
     const int page = bt[k / page_size];
     const size_t row = (((size_t)page * nkv + kvh) * page_size + (k % page_size)) * D;
@@ -270,7 +283,7 @@ template <typename T, int D>
 int launch_rows(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                 const int* block_tables, int max_pages, const int* seq_of_token, const int* positions,
                 void* out, int out_row_stride, int n_tokens, int nq, int nkv, int page_size, int window,
-                float scale, cudaStream_t s) {
+                int keep_first, float scale, cudaStream_t s) {
   const size_t smem = (size_t)(kRowWarps * D + kRowWarps * 32 * (D + 1)) * sizeof(float);
   auto kern = attention_rows_kernel<T, D>;
   if (smem > 48 * 1024) {
@@ -280,7 +293,7 @@ int launch_rows(const void* q, int q_row_stride, const void* k_pages, const void
   dim3 grid((n_tokens + kRowWarps - 1) / kRowWarps, nq);
   launch_chained(kern, dim3(grid), dim3(kRowWarps * 32), smem, s, (const T*)q, q_row_stride, (const T*)k_pages, (const T*)v_pages,
       block_tables, max_pages, seq_of_token, positions, (T*)out, out_row_stride, n_tokens, nq, nkv,
-      page_size, window, scale);
+      page_size, window, keep_first, scale);
   return check_launch("attention_rows");
 }
 
@@ -288,7 +301,7 @@ template <typename T, int D>
 int launch_decode(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                   const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                   void* out, int out_row_stride, float* part_acc, float* part_ml, int max_splits, int n_seqs,
-                  int nq, int nkv, int page_size, int window, int split_keys, float scale, cudaStream_t s) {
+                  int nq, int nkv, int page_size, int window, int keep_first, int split_keys, float scale, cudaStream_t s) {
   const size_t smem =
       (size_t)(D + kDecodeWarps * 32 * (D + 1) + kDecodeWarps * (D + 2)) * sizeof(float);
   auto kern = attention_decode_split_kernel<T, D>;
@@ -299,7 +312,7 @@ int launch_decode(const void* q, int q_row_stride, const void* k_pages, const vo
   dim3 grid(max_splits, nq, n_seqs);
   launch_chained(kern, dim3(grid), dim3(kDecodeWarps * 32), smem, s, (const T*)q, q_row_stride, (const T*)k_pages,
       (const T*)v_pages, block_tables, max_pages, token_of_seq, positions, part_acc, part_ml, max_splits,
-      nq, nkv, page_size, window, split_keys, scale);
+      nq, nkv, page_size, window, keep_first, split_keys, scale);
   int rc = check_launch("attention_decode_split");
   if (rc) return rc;
   launch_chained(attention_decode_combine_kernel<T>, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq,
@@ -334,14 +347,14 @@ int check_common(const char* who, int nq, int nkv, int head_dim, int page_size, 
 ERB_EXPORT int erb_attention_rows(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                   const int* block_tables, int max_pages, const int* seq_of_token,
                                   const int* positions, void* out, int out_row_stride, int n_tokens, int nq,
-                                  int nkv, int head_dim, int page_size, int window, float scale,
+                                  int nkv, int head_dim, int page_size, int window, int keep_first, float scale,
                                   void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   int rc = check_common("attention_rows", nq, nkv, head_dim, page_size, max_pages);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
   ERB_DISPATCH_D(launch_rows, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, seq_of_token,
-                 positions, out, out_row_stride, n_tokens, nq, nkv, page_size, window, scale, s)
+                 positions, out, out_row_stride, n_tokens, nq, nkv, page_size, window, window > 0 ? keep_first : 0, scale, s)
   return fail(ERB_ERR_UNSUPPORTED, "attention_rows: head_dim %d", head_dim);
 }
 
@@ -353,7 +366,7 @@ ERB_EXPORT int erb_attention_decode(const void* q, int q_row_stride, const void*
                                     const int* token_of_seq, const int* positions, void* out,
                                     int out_row_stride, float* part_acc, float* part_ml, int max_splits,
                                     int n_seqs, int nq, int nkv, int head_dim, int page_size, int window,
-                                    int split_keys, float scale, void* stream) {
+                                    int keep_first, int split_keys, float scale, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
   int rc = check_common("attention_decode", nq, nkv, head_dim, page_size, max_pages);
   if (rc) return rc;
@@ -363,7 +376,7 @@ ERB_EXPORT int erb_attention_decode(const void* q, int q_row_stride, const void*
   cudaStream_t s = (cudaStream_t)stream;
   ERB_DISPATCH_D(launch_decode, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                  positions, out, out_row_stride, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size,
-                 window, split_keys, scale, s)
+                 window, window > 0 ? keep_first : 0, split_keys, scale, s)
   return fail(ERB_ERR_UNSUPPORTED, "attention_decode: head_dim %d", head_dim);
 }
 
@@ -426,5 +439,5 @@ ERB_EXPORT int erb_attention_decode_static(const void* q, int q_row_stride, cons
   float* part_ml = base + (size_t)n_seqs * nq * max_splits * head_dim;
   return erb_attention_decode(q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                               positions, out, out_row_stride, part_acc, part_ml, max_splits, n_seqs, nq, nkv,
-                              head_dim, page_size, window, split_keys, scale, stream);
+                              head_dim, page_size, window, 0, split_keys, scale, stream);
 }

@@ -103,6 +103,26 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 #endif
 }
 
+// gelu(g) * u with the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))), in float.  Every
+// kernel that gates this way calls this, so that they agree to the bit.
+__device__ __forceinline__ float gelu_tanh_mul(float g, float u) {
+  const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+  return 0.5f * g * (1.f + tanhf(inner)) * u;
+}
+
+// The gate of a gated unit with bounded branches: g = min(g, limit), u = clamp(u, -limit, limit) for limit > 0;
+// act 0: g * sigmoid(alpha g) * (u + shift); act 1: gelu_tanh(g) * (u + shift).
+#define ERB_GLU_SIGMOID 0
+#define ERB_GLU_GELU_TANH 1
+__device__ __forceinline__ float glu_gate(float g, float u, int act, float limit, float alpha, float shift) {
+  if (limit > 0.f) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+  }
+  if (act == ERB_GLU_GELU_TANH) return gelu_tanh_mul(g, u + shift);
+  return g / (1.f + expf(-alpha * g)) * (u + shift);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

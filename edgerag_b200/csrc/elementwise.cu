@@ -691,29 +691,26 @@ ERB_EXPORT int erb_resolve_ids(int* ids, int n, const int* fed, int n_fed, void*
 // ---------------------------------------------------------------------------------------------
 // A gated unit with bounded branches: with g = min(gate, limit) and u = clamp(up, -limit, limit),
 //   out[t, i] = g * sigmoid(alpha * g) * (u + shift),      gate = gate_up[t, i], up = gate_up[t, I + i],
-// computed in float.  limit <= 0 leaves both branches unbounded; (alpha, shift) = (1, 0) is SwiGLU.
+// computed in float.  limit <= 0 leaves both branches unbounded; (alpha, shift) = (1, 0) is SwiGLU.  `act` 1 puts
+// the tanh form of gelu in the place of g * sigmoid(alpha * g) (see glu_gate).
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void glu_bounded_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total,
-                                   float limit, float alpha, float shift) {
+                                   float limit, float alpha, float shift, int act) {
   chain_wait();
   size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / inter;
   const int i = (int)(idx % inter);
   const T* row = gate_up + t * 2 * (size_t)inter;
-  float g = Elem<T>::load(row + i), u = Elem<T>::load(row + inter + i);
-  if (limit > 0.f) {
-    g = fminf(g, limit);
-    u = fminf(fmaxf(u, -limit), limit);
-  }
-  Elem<T>::store(out + idx, g / (1.f + expf(-alpha * g)) * (u + shift));
+  const float g = Elem<T>::load(row + i), u = Elem<T>::load(row + inter + i);
+  Elem<T>::store(out + idx, glu_gate(g, u, act, limit, alpha, shift));
 }
 
 // The same on 16-byte groups (the intermediate size a multiple of the group, rows 16-byte aligned).
 template <typename T>
 __global__ void glu_bounded_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t groups,
-                                       float limit, float alpha, float shift) {
+                                       float limit, float alpha, float shift, int act) {
   chain_wait();
   constexpr int N = Vec16<T>::N;
   const size_t gidx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -726,30 +723,23 @@ __global__ void glu_bounded_vec_kernel(const T* __restrict__ gate_up, T* __restr
   Vec16<T>::load(row + i, g);
   Vec16<T>::load(row + inter + i, u);
 #pragma unroll
-  for (int j = 0; j < N; ++j) {
-    float gg = g[j], uu = u[j];
-    if (limit > 0.f) {
-      gg = fminf(gg, limit);
-      uu = fminf(fmaxf(uu, -limit), limit);
-    }
-    g[j] = gg / (1.f + expf(-alpha * gg)) * (uu + shift);
-  }
+  for (int j = 0; j < N; ++j) g[j] = glu_gate(g[j], u[j], act, limit, alpha, shift);
   Vec16<T>::store(out + t * (size_t)inter + i, g);
 }
 
 ERB_EXPORT int erb_glu_bounded(const void* gate_up, void* out, int n_tokens, int inter, float limit, float alpha,
-                               float shift, void* stream) {
+                               float shift, int act, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   if (inter <= 0) return fail(ERB_ERR_ARG, "glu_bounded: bad intermediate size");
   const size_t total = (size_t)n_tokens * inter;
   if (inter % Vec16<elem_t>::N == 0 && !((uintptr_t)gate_up & 15) && !((uintptr_t)out & 15)) {
     const size_t groups = total / Vec16<elem_t>::N;
     launch_chained(glu_bounded_vec_kernel<elem_t>, dim3((unsigned)((groups + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
-                   (const elem_t*)gate_up, (elem_t*)out, inter, groups, limit, alpha, shift);
+                   (const elem_t*)gate_up, (elem_t*)out, inter, groups, limit, alpha, shift, act);
     return check_launch("glu_bounded");
   }
   launch_chained(glu_bounded_kernel<elem_t>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
-                 (const elem_t*)gate_up, (elem_t*)out, inter, total, limit, alpha, shift);
+                 (const elem_t*)gate_up, (elem_t*)out, inter, total, limit, alpha, shift, act);
   return check_launch("glu_bounded");
 }
 
@@ -769,4 +759,239 @@ ERB_EXPORT int erb_softcap(float* x, int n_rows, int width, int stride, float ca
   if (y > 64) y = 64;
   launch_chained(softcap_kernel, dim3(n_rows, y), dim3(256), 0, (cudaStream_t)stream, x, width, stride, cap);
   return check_launch("softcap");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Residual add between two layer norms (weight and bias; the variance is the mean of the squared
+// deviations from the mean, both taken in float over the whole row):
+//   d = delta[row]                       rows of T, or float partial sums added in order and rounded to T
+//   d = LN(d; post_w, post_b)            when post_w is given: the norm that closes a sublayer, kept in float
+//   r = hidden[row] + d                  stored back when `write_back`
+//   out[o] = round_T(LN(r; w, b))        when w is given; round_T(r) when only `out` is; nothing without `out`
+// `rows`, when given, selects the rows of hidden/delta that are read; `out` rows are `out_ld` elements apart.
+// One block per row; the row is parked in shared memory between the passes.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+add_layernorm_kernel(float* __restrict__ hidden, const T* __restrict__ delta, const float* __restrict__ parts, int n_parts,
+                     size_t part_stride, const float* __restrict__ post_w, const float* __restrict__ post_b, float post_eps,
+                     const float* __restrict__ w, const float* __restrict__ b, float eps, T* __restrict__ out, int out_ld,
+                     const int* __restrict__ rows, int width, int write_back) {
+  chain_wait();
+  extern __shared__ float row_cache[];  // width floats, then 32 of scratch
+  float* scratch = row_cache + width;
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* h = hidden + (size_t)r * width;
+  const T* d = delta ? delta + (size_t)r * width : nullptr;
+  const float* ps = parts ? parts + (size_t)r * width : nullptr;
+  const float inv_w = 1.f / (float)width;
+  const bool has_delta = d || ps;
+  if (has_delta) {
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float v;
+      if (d) {
+        v = Elem<T>::load(d + i);
+      } else {
+        v = ps[i];
+        for (int sp = 1; sp < n_parts; ++sp) v += ps[sp * part_stride + i];
+        v = Elem<T>::round(v);
+      }
+      row_cache[i] = v;
+      sum += v;
+    }
+    if (post_w) {
+      const float mean = block_sum(sum, scratch) * inv_w;
+      float sq = 0.f;
+      for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float c = row_cache[i] - mean;
+        sq += c * c;
+      }
+      const float rs = rsqrtf(block_sum(sq, scratch) * inv_w + post_eps);
+      for (int i = threadIdx.x; i < width; i += blockDim.x)
+        row_cache[i] = (row_cache[i] - mean) * rs * post_w[i] + post_b[i];
+    }
+  }
+  float sum = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float v = h[i];
+    if (has_delta) {
+      v += row_cache[i];
+      if (write_back) h[i] = v;
+    }
+    row_cache[i] = v;
+    sum += v;
+  }
+  if (!out) return;
+  T* y = out + (size_t)o * out_ld;
+  if (!w) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) Elem<T>::store(y + i, row_cache[i]);
+    return;
+  }
+  const float mean = block_sum(sum, scratch) * inv_w;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float c = row_cache[i] - mean;
+    sq += c * c;
+  }
+  const float rs = rsqrtf(block_sum(sq, scratch) * inv_w + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    Elem<T>::store(y + i, (row_cache[i] - mean) * rs * w[i] + b[i]);
+}
+
+// delta: rows of the element type, or (n_parts > 0) float partial sums [n_parts][rows of hidden][width].
+ERB_EXPORT int erb_add_layernorm(void* hidden, const void* delta, int n_parts, long long part_stride, const float* post_w,
+                                 const float* post_b, float post_eps, const float* w, const float* b, float eps, void* out,
+                                 int out_ld, const int* rows, int n_rows, int width, int write_back, void* stream) {
+  if (n_rows <= 0) return ERB_OK;
+  if (width <= 0 || (out && out_ld < width) || (w && !b) || (post_w && !post_b) || (post_w && !delta))
+    return fail(ERB_ERR_ARG, "add_layernorm: bad sizes or a weight without its bias");
+  const size_t smem = (size_t)(width + 32) * sizeof(float);
+  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "add_layernorm: width %d does not fit shared memory", width);
+  auto kern = add_layernorm_kernel<elem_t>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(ERB_ERR_CUDA, "add_layernorm: %s", cudaGetErrorString(e));
+  }
+  const int threads = width >= 1024 ? 256 : (width >= 512 ? 128 : 64);
+  launch_chained(kern, dim3(n_rows), dim3(threads), smem, (cudaStream_t)stream,
+                 (float*)hidden, n_parts > 0 ? (const elem_t*)nullptr : (const elem_t*)delta,
+                 n_parts > 0 ? (const float*)delta : (const float*)nullptr, n_parts, (size_t)part_stride, post_w, post_b, post_eps,
+                 w, b, eps, (elem_t*)out, out_ld, rows, width, write_back);
+  return check_launch("add_layernorm");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Rows of the float stream cast to T into a wider buffer: dst[t, :width] = round_T(src[t, :]), rows `dst_ld` apart.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void cast_rows_kernel(const float* __restrict__ src, T* __restrict__ dst, int width, int dst_ld, size_t total) {
+  chain_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / width;
+  const int i = (int)(idx % width);
+  Elem<T>::store(dst + t * dst_ld + i, src[idx]);
+}
+
+ERB_EXPORT int erb_cast_rows(const float* src, void* dst, int n_rows, int width, int dst_ld, void* stream) {
+  if (n_rows <= 0) return ERB_OK;
+  if (width <= 0 || dst_ld < width) return fail(ERB_ERR_ARG, "cast_rows: bad sizes");
+  const size_t total = (size_t)n_rows * width;
+  launch_chained(cast_rows_kernel<elem_t>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, src,
+                 (elem_t*)dst, width, dst_ld, total);
+  return check_launch("cast_rows");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The stream set anew: hidden[t, i] = float(y[t, i]) + vec[i] (a product's rows plus one vector for all rows).
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void stream_set_kernel(float* __restrict__ hidden, const T* __restrict__ y, const float* __restrict__ vec, int width,
+                                  size_t total) {
+  chain_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  hidden[idx] = Elem<T>::load(y + idx) + (vec ? vec[idx % width] : 0.f);
+}
+
+ERB_EXPORT int erb_stream_set(float* hidden, const void* y, const float* vec, int n_rows, int width, void* stream) {
+  if (n_rows <= 0) return ERB_OK;
+  const size_t total = (size_t)n_rows * width;
+  launch_chained(stream_set_kernel<elem_t>, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, hidden,
+                 (const elem_t*)y, vec, width, total);
+  return check_launch("stream_set");
+}
+
+// ---------------------------------------------------------------------------------------------
+// Queries and keys made ready for attention, one warp per (token, head) of a row [q heads | k heads | v heads]:
+//   x = row[head] (+ bias[head])                                   in float
+//   a k head with `values_are_keys`: the token's value row in the cache is round_T(x) (before norm and turn)
+//   x = x * rsqrt(mean(x^2) + eps) * norm_w                         when norm weights are given (q_norm for q heads,
+//                                                                   k_norm for k heads, one vector for all heads)
+//   the first rot_dim entries turned by angle[i] = position * inv_freq[i]: pairs (2i, 2i + 1) when `pairs`, else
+//   (i, i + rot_dim / 2); the rest passes
+//   q heads are written back in place, k heads to the token's cache slot, v heads (absent with `values_are_keys`)
+//   to the slot as they are.  slot = page * page_size + offset, negative: the token writes no key or value.
+// ---------------------------------------------------------------------------------------------
+constexpr int kPrepWarps = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+qk_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                  const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                  const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim, int pairs,
+                  const int* __restrict__ slots, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nq, int nkv,
+                  int D, int page_size, int values_are_keys) {
+  chain_wait();
+  extern __shared__ float prep_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* x = prep_smem + warp * D;
+  const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
+  const long long item = (long long)blockIdx.x * kPrepWarps + warp;
+  if (item >= (long long)n_tokens * heads) return;
+  const int t = (int)(item / heads), head = (int)(item % heads);
+  T* src = qkv + (size_t)t * ld + (size_t)head * D;
+  const int slot = slots ? slots[t] : -1;
+  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  if (head >= nq + nkv) {                        // a value head: copied to the cache as it is
+    if (slot < 0 || !v_pages) return;
+    T* dst = v_pages + ((page * nkv + (head - nq - nkv)) * page_size + off) * D;
+    for (int i = lane; i < D; i += 32) dst[i] = src[i];
+    return;
+  }
+  const bool is_q = head < nq;
+  const float* bias = is_q ? q_bias : k_bias;
+  if (bias) bias += (size_t)(is_q ? head : head - nq) * D;
+  const float* nw = is_q ? q_norm : k_norm;
+  const bool store_kv = !is_q && slot >= 0 && k_pages;
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    const float v = Elem<T>::load(src + i) + (bias ? bias[i] : 0.f);
+    x[i] = v;
+    ss += v * v;
+  }
+  if (!is_q && values_are_keys && store_kv && v_pages) {
+    T* dst = v_pages + ((page * nkv + (head - nq)) * page_size + off) * D;
+    for (int i = lane; i < D; i += 32) Elem<T>::store(dst + i, x[i]);
+  }
+  if (nw) {
+    const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+    for (int i = lane; i < D; i += 32) x[i] = x[i] * rs * nw[i];
+  }
+  __syncwarp();
+  T* dst = is_q ? src : (store_kv ? k_pages + ((page * nkv + (head - nq)) * page_size + off) * D : nullptr);
+  if (!dst) return;
+  const float pos = (float)positions[t];
+  const int half = rot_dim / 2;
+  for (int i = lane; i < half; i += 32) {
+    const int a = pairs ? 2 * i : i, b = pairs ? 2 * i + 1 : i + half;
+    float sn, cs, lo, hi;
+    sincosf(pos * inv_freq[i], &sn, &cs);
+    rotate_pair(x[a], x[b], cs, sn, lo, hi);
+    Elem<T>::store(dst + a, lo);
+    Elem<T>::store(dst + b, hi);
+  }
+  if (!is_q || bias || nw)
+    for (int i = rot_dim + lane; i < D; i += 32) Elem<T>::store(dst + i, x[i]);
+}
+
+ERB_EXPORT int erb_qk_prepare(void* qkv, int ld, const float* q_bias, const float* k_bias, const float* q_norm,
+                              const float* k_norm, float eps, const int* positions, const float* inv_freq, int rot_dim,
+                              int pairs, const int* slots, void* k_pages, void* v_pages, int n_tokens, int nq, int nkv,
+                              int head_dim, int page_size, int values_are_keys, void* stream) {
+  if (n_tokens <= 0) return ERB_OK;
+  if (nq <= 0 || nkv <= 0 || head_dim <= 0 || rot_dim < 0 || rot_dim > head_dim || rot_dim % 2 || page_size <= 0 || !positions ||
+      (rot_dim && !inv_freq))
+    return fail(ERB_ERR_ARG, "qk_prepare: bad sizes (rot_dim %d of head_dim %d)", rot_dim, head_dim);
+  if (ld < (nq + nkv + (values_are_keys ? 0 : nkv)) * head_dim) return fail(ERB_ERR_ARG, "qk_prepare: rows too narrow");
+  const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
+  const long long items = (long long)n_tokens * heads;
+  const size_t smem = (size_t)kPrepWarps * head_dim * sizeof(float);
+  if (smem > 48 * 1024) return fail(ERB_ERR_UNSUPPORTED, "qk_prepare: head_dim %d", head_dim);
+  launch_chained(qk_prepare_kernel<elem_t>, dim3((unsigned)((items + kPrepWarps - 1) / kPrepWarps)), dim3(kPrepWarps * 32), smem,
+                 (cudaStream_t)stream, (elem_t*)qkv, ld, q_bias, k_bias, q_norm, k_norm, eps, positions, inv_freq, rot_dim, pairs,
+                 slots, (elem_t*)k_pages, (elem_t*)v_pages, n_tokens, nq, nkv, head_dim, page_size, values_are_keys);
+  return check_launch("qk_prepare");
 }

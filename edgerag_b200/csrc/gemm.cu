@@ -345,6 +345,7 @@ struct RopeArgs {
   // MODE 2 only: g * sigmoid(alpha g) * (u + shift) with g = min(g, limit), u = clamp(u, -limit, limit) when limit > 0;
   // the defaults are the SwiGLU gate
   float glu_limit = 0.f, glu_alpha = 1.f, glu_shift = 0.f;
+  int glu_act = 0;             // ERB_GLU_SIGMOID or ERB_GLU_GELU_TANH (see glu_gate)
 };
 
 // NT: tiles of 8 rows of `a`; RT: tiles of 16 rows of w per block; kSkWarps: warps per block;
@@ -460,12 +461,8 @@ linear_skinny_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* _
       if constexpr (GLU) {
         const int n = n0 + rr;
         float act;
-        if (ra.glu_limit > 0.f || ra.glu_alpha != 1.f || ra.glu_shift != 0.f) {     // the bounded gate, as its own kernel writes it
-          if (ra.glu_limit > 0.f) {
-            v0 = fminf(v0, ra.glu_limit);
-            v1 = fminf(fmaxf(v1, -ra.glu_limit), ra.glu_limit);
-          }
-          act = v0 / (1.f + expf(-ra.glu_alpha * v0)) * (v1 + ra.glu_shift);
+        if (ra.glu_limit > 0.f || ra.glu_alpha != 1.f || ra.glu_shift != 0.f || ra.glu_act != 0) {     // the bounded gate, as its own kernel writes it
+          act = glu_gate(v0, v1, ra.glu_act, ra.glu_limit, ra.glu_alpha, ra.glu_shift);
         } else {
           act = silu_mul(v0, v1);
         }
@@ -690,12 +687,12 @@ ERB_EXPORT int erb_linear_skinny_glu(const void* a, const void* w, void* out, in
 // The same with the bounded gate of `glu_bounded_kernel` (elementwise.cu) in the epilogue:
 // out = g * sigmoid(alpha g) * (u + shift), g = min(g, limit), u = clamp(u, -limit, limit) for limit > 0.
 ERB_EXPORT int erb_linear_skinny_glu_bounded(const void* a, const void* w, void* out, int M, int N, int K, int lda, int ldw,
-                                             int ldo, float limit, float alpha, float shift, void* stream) {
+                                             int ldo, float limit, float alpha, float shift, int act, void* stream) {
   if (M <= 0) return ERB_OK;
   int rc = check_skinny("linear_skinny_glu_bounded", a, w, M, N, K, lda, ldw, ldo);
   if (rc) return rc;
   RopeArgs ra{};
-  ra.glu_limit = limit; ra.glu_alpha = alpha; ra.glu_shift = shift;
+  ra.glu_limit = limit; ra.glu_alpha = alpha; ra.glu_shift = shift; ra.glu_act = act;
   return launch_skinny_mode<2>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, out, M, N, K, lda, ldw, ldo,
                                (cudaStream_t)stream, ra);
 }

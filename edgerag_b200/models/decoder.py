@@ -12,7 +12,7 @@ import torch
 
 from ..cache.manager import CacheLayout, KVGroupSpec, StateSpec
 from ..ops import kernels
-from ..parts.base import _REGISTRY, LayerCall, ModelPlan, Part, WeightSpec, build_part
+from ..parts.base import _REGISTRY, LayerCall, ModelPlan, Part, StreamCall, WeightSpec, build_part, settle_update
 
 
 class DecoderModel:
@@ -47,7 +47,12 @@ class DecoderModel:
             self._owners.append((plan.final_norm.prefix, self.final_norm))
         self.head = build_part("head", plan.head, dtype, device)
         self._owners.append((plan.head.prefix, self.head))
-        self.schedule: list[LayerCall] = list(plan.schedule)
+        self.stream_ops = [build_part("stream", spec, dtype, device) for spec in plan.stream_ops]
+        self._owners += [(spec.prefix, op) for spec, op in zip(plan.stream_ops, self.stream_ops)]
+        self.schedule: list[LayerCall | StreamCall] = list(plan.schedule)
+        for call in self.schedule:
+            if isinstance(call, StreamCall) and not 0 <= call.op < len(self.stream_ops):
+                raise ValueError(f"the run order names stream operation {call.op}, the plan has {len(self.stream_ops)}")
         self.cache_layout = self._derive_cache_layout()
         #: every part may be captured in a CUDA graph (an attention mixer also vouches for its position encoding)
         self.graph_safe = all(part.graph_safe for _, part in self._owners) and all(
@@ -57,22 +62,23 @@ class DecoderModel:
     # --- cache needs ------------------------------------------------------------------------------
 
     def _derive_cache_layout(self) -> CacheLayout:
-        n_cache_layers = 1 + max((c.cache_layer for c in self.schedule if c.cache_layer is not None), default=-1)
+        calls = [c for c in self.schedule if isinstance(c, LayerCall)]
+        n_cache_layers = 1 + max((c.cache_layer for c in calls if c.cache_layer is not None), default=-1)
         owner: list[int | None] = [None] * n_cache_layers
-        for call in self.schedule:
+        for call in calls:
             if call.cache_layer is not None and call.writes_cache:
                 if owner[call.cache_layer] is not None:
                     raise ValueError(f"cache layer {call.cache_layer} is written by two calls of the run order")
                 owner[call.cache_layer] = call.layer
         layout = CacheLayout(placement=[None] * n_cache_layers)
-        keys: list[tuple[int, int, int, int | None]] = []
+        keys: list[tuple] = []
         counts: list[int] = []
         for cl, layer in enumerate(owner):
             if layer is None:
                 raise ValueError(f"cache layer {cl} is read but never written")
             spec = self.blocks[layer].mixer.cache_spec()
             if isinstance(spec, KVGroupSpec):
-                key = (spec.n_kv_heads, spec.head_dim, spec.window, spec.v_head_dim)
+                key = (spec.n_kv_heads, spec.head_dim, spec.window, spec.v_head_dim, spec.keep_first)
                 if key not in keys:
                     keys.append(key)
                     counts.append(0)
@@ -113,9 +119,15 @@ class DecoderModel:
         hidden = ctx.buf("model.hidden", (n, self.hidden_size), torch.float32)
         self.embedding.forward(ctx, hidden)
         ctx.stream_written = kernels.launches()      # (the embedding wrote the residual stream: see the block)
+        for op in self.stream_ops:
+            op.begin(ctx, hidden)
         delta = None
         for call in self.schedule:
             before = ctx.stream_written
+            if isinstance(call, StreamCall):
+                delta = self.stream_ops[call.op].forward(hidden, delta, ctx, call)
+                ctx.stream_written = float("inf")
+                continue
             delta = self.blocks[call.layer].forward(hidden, delta, ctx, call)
             if ctx.stream_written == before:      # a block that keeps no account of its writes to the stream:
                 ctx.stream_written = float("inf")  # nobody may assume that the stream has settled
@@ -127,8 +139,7 @@ class DecoderModel:
             self.final_norm.forward(hidden, y, delta, rows=ctx.want_rows, write_back=False,
                                     settled=kernels.launches() > ctx.stream_written)
         else:
-            if delta is not None:
-                kernels.residual_add(hidden, delta, self.dtype)
+            settle_update(hidden, delta, self.dtype)
             kernels.gather_cast(hidden, y, ctx.want_rows)
         logits = ctx.buf("model.logits", (w, self.logits_stride), torch.float32)[:, : self.vocab_size]
         self.head.forward(y, logits)

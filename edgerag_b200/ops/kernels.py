@@ -38,7 +38,7 @@ _SIGNATURES = {
     "erb_linear_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_skinny_glu": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_linear_skinny_glu_bounded": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
-                                      c_float, c_void_p],
+                                      c_float, c_int, c_void_p],
     "erb_linear_skinny_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_linear_tc": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -53,10 +53,10 @@ _SIGNATURES = {
     "erb_linear_tc_rope": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "erb_attention_rows": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "erb_attention_decode": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                              c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_float, c_void_p],
+                             c_int, c_int, c_int, c_float, c_void_p],
     "erb_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                  c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -66,7 +66,13 @@ _SIGNATURES = {
     "erb_attention_decode_gqa": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_void_p, c_void_p, c_void_p],
-    "erb_glu_bounded": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_void_p],
+    "erb_glu_bounded": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
+    "erb_add_layernorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float,
+                          c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "erb_cast_rows": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "erb_stream_set": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "erb_qk_prepare": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "erb_softcap": [c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "erb_linear_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p],
@@ -225,6 +231,104 @@ def residual_add(hidden: torch.Tensor, delta: torch.Tensor, dtype: torch.dtype |
           hidden.numel(), _stream())
 
 
+def add_layernorm(hidden: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | None, out: torch.Tensor | None,
+                  eps: float, delta: torch.Tensor | None = None, post: tuple[torch.Tensor, torch.Tensor, float] | None = None,
+                  rows: torch.Tensor | None = None, write_back: bool = True) -> None:
+    """The residual add between two layer norms (weight and bias, statistics in float): with ``post = (w, b, eps)``
+    the update is normed first, ``d = LN(delta; w, b)`` kept in float; ``hidden += d`` in place when ``write_back``;
+    ``out = LN(hidden (+ d); weight, bias)`` rounded once, or the plain cast of the sum where ``weight`` is None, or
+    nothing where ``out`` is None.  ``delta``: rows of the element type or float32 partial sums ``[parts, rows,
+    width]`` (added in order, rounded to the element type once).  ``out`` may be a view with unit inner stride."""
+    _need(hidden, "hidden", torch.float32); _need(weight, "weight", torch.float32); _need(bias, "bias", torch.float32)
+    _need(out, "out", contiguous=False); _need(rows, "rows", torch.int32)
+    h = hidden.shape[1]
+    in_parts = delta is not None and delta.dim() == 3
+    elem = out.dtype if out is not None else (delta.dtype if delta is not None and not in_parts else None)
+    if elem is None:
+        raise KernelError("add_layernorm: neither an output nor rows of an update name the element type")
+    _need(delta, "delta", torch.float32 if in_parts else elem)
+    if delta is not None and delta.shape[-2:] != hidden.shape:
+        raise KernelError("add_layernorm: delta and hidden disagree")
+    if (weight is None) != (bias is None) or (weight is not None and (weight.numel() != h or bias.numel() != h)):
+        raise KernelError("add_layernorm: weight and bias come together and have the row's width")
+    pw = pb = None
+    peps = 0.0
+    if post is not None:
+        pw, pb, peps = post
+        _need(pw, "post weight", torch.float32); _need(pb, "post bias", torch.float32)
+        if delta is None or pw.numel() != h or pb.numel() != h:
+            raise KernelError("add_layernorm: a norm of the update needs the update and vectors of the row's width")
+    if out is not None:
+        n = out.shape[0]
+        if out.shape[1] != h or out.stride(1) != 1:
+            raise KernelError("add_layernorm: out must be [rows, width] with unit inner stride")
+        if rows is None and n != hidden.shape[0]:
+            raise KernelError("add_layernorm: out rows differ from hidden rows")
+        if rows is not None and rows.numel() < n:
+            raise KernelError("add_layernorm: fewer row indices than output rows")
+        out_ld = out.stride(0) if n > 1 else max(h, out.stride(0))
+    else:
+        n, out_ld = hidden.shape[0], h
+        if rows is not None:
+            raise KernelError("add_layernorm: a selection of rows needs an output")
+    _call(_fn("elementwise", _ELEM[elem], "erb_add_layernorm"), hidden.data_ptr(), _ptr(delta), delta.shape[0] if in_parts else 0,
+          delta.stride(0) if in_parts else 0, _ptr(pw), _ptr(pb), float(peps), _ptr(weight), _ptr(bias), float(eps), _ptr(out),
+          int(out_ld), _ptr(rows), n, h, int(write_back and rows is None), _stream())
+
+
+def cast_rows(src: torch.Tensor, dst: torch.Tensor) -> None:
+    """dst[t, :] = src[t, :] rounded to ``dst``'s element type; ``src`` float32 rows, ``dst`` a view with unit inner stride."""
+    _need(src, "src", torch.float32); _need(dst, "dst", contiguous=False)
+    n, width = src.shape
+    if dst.shape != (n, width) or dst.stride(1) != 1:
+        raise KernelError("cast_rows: shapes disagree")
+    _call(_fn("elementwise", _elem(dst), "erb_cast_rows"), src.data_ptr(), dst.data_ptr(), n, width,
+          dst.stride(0) if n > 1 else max(width, dst.stride(0)), _stream())
+
+
+def stream_set(hidden: torch.Tensor, y: torch.Tensor, vec: torch.Tensor | None = None) -> None:
+    """hidden[t, :] = float(y[t, :]) + vec: the residual stream set anew from a product's rows and one vector."""
+    _need(hidden, "hidden", torch.float32); _need(y, "y"); _need(vec, "vec", torch.float32)
+    if y.shape != hidden.shape or (vec is not None and vec.numel() != hidden.shape[1]):
+        raise KernelError("stream_set: shapes disagree")
+    _call(_fn("elementwise", _elem(y), "erb_stream_set"), hidden.data_ptr(), y.data_ptr(), _ptr(vec), hidden.shape[0],
+          hidden.shape[1], _stream())
+
+
+def qk_prepare(qkv: torch.Tensor, positions: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int, *,
+               q_bias: torch.Tensor | None = None, k_bias: torch.Tensor | None = None, q_norm: torch.Tensor | None = None,
+               k_norm: torch.Tensor | None = None, eps: float = 0.0, inv_freq: torch.Tensor | None = None, rot_dim: int = 0,
+               pairs: bool = False, values_are_keys: bool = False, slots: torch.Tensor | None = None,
+               k_pages: torch.Tensor | None = None, v_pages: torch.Tensor | None = None, page_size: int = 0) -> None:
+    """Queries and keys made ready for attention, per head of each row ``[q heads | k heads (| v heads)]`` of ``qkv``:
+    bias added, (``values_are_keys``: the result is the token's cached value), unit RMS times a weight shared by the
+    heads (``q_norm`` / ``k_norm``), the first ``rot_dim`` entries turned by ``position * inv_freq[i]`` (neighbouring
+    pairs ``(2i, 2i + 1)`` with ``pairs``, else ``(i, i + rot_dim / 2)``).  q is rewritten in place; k (and v) go to
+    the token's cache slot (``slots``: ``page * page_size + offset``, negative: nothing is written)."""
+    _need(qkv, "qkv", contiguous=False); _need(positions, "positions", torch.int32)
+    for name, t in (("q_bias", q_bias), ("k_bias", k_bias), ("q_norm", q_norm), ("k_norm", k_norm), ("inv_freq", inv_freq)):
+        _need(t, name, torch.float32)
+    _need(slots, "slots", torch.int32); _need(k_pages, "k_pages", qkv.dtype); _need(v_pages, "v_pages", qkv.dtype)
+    n = qkv.shape[0]
+    heads = n_q_heads + n_kv_heads * (1 if values_are_keys else 2)
+    if qkv.stride(1) != 1 or qkv.shape[1] < heads * head_dim or positions.numel() < n:
+        raise KernelError("qk_prepare: qkv width or positions disagree with the head counts")
+    if (q_bias is not None and q_bias.numel() != n_q_heads * head_dim) or (k_bias is not None and k_bias.numel() != n_kv_heads * head_dim) \
+            or (q_norm is not None and q_norm.numel() != head_dim) or (k_norm is not None and k_norm.numel() != head_dim):
+        raise KernelError("qk_prepare: a bias or norm weight has the wrong size")
+    if rot_dim and (inv_freq is None or inv_freq.numel() != rot_dim // 2):
+        raise KernelError("qk_prepare: inv_freq must hold rot_dim / 2 values")
+    if k_pages is not None:
+        if v_pages is None or slots is None or slots.numel() < n or page_size <= 0:
+            raise KernelError("qk_prepare: a cache write needs k_pages, v_pages, slots and the page size")
+        if tuple(k_pages.shape[1:]) != (n_kv_heads, page_size, head_dim) or k_pages.shape != v_pages.shape:
+            raise KernelError("qk_prepare: page layout is not [pages, kv heads, page_size, head_dim]")
+    _call(_fn("elementwise", _elem(qkv), "erb_qk_prepare"), qkv.data_ptr(), qkv.stride(0) if n > 1 else qkv.shape[1], _ptr(q_bias),
+          _ptr(k_bias), _ptr(q_norm), _ptr(k_norm), float(eps), positions.data_ptr(), _ptr(inv_freq), int(rot_dim), int(pairs),
+          _ptr(slots), _ptr(k_pages), _ptr(v_pages), n, n_q_heads, n_kv_heads, head_dim, max(1, int(page_size)),
+          int(values_are_keys), _stream())
+
+
 def resolve_ids(ids: torch.Tensor, fed: torch.Tensor, dtype: torch.dtype = torch.bfloat16) -> None:
     """Replace every id t < 0 of ``ids`` (int32, in place) by ``fed[-t - 1]``: tokens of the step
     before that are still on the device.  ``dtype`` only picks the library that holds the kernel
@@ -276,15 +380,20 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     _call(_fn("elementwise", _elem(out), "erb_swiglu"), gate_up.data_ptr(), out.data_ptr(), n, inter, _stream())
 
 
-def glu_bounded(gate_up: torch.Tensor, out: torch.Tensor, limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0) -> None:
+GLU_ACTS = {"sigmoid": 0, "gelu_tanh": 1}
+
+
+def glu_bounded(gate_up: torch.Tensor, out: torch.Tensor, limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0,
+                act: str = "sigmoid") -> None:
     """out[t, i] = g * sigmoid(alpha * g) * (u + shift) with g = min(gate_up[t, i], limit) and
-    u = clamp(gate_up[t, I + i], -limit, limit); ``limit <= 0`` bounds nothing."""
+    u = clamp(gate_up[t, I + i], -limit, limit); ``limit <= 0`` bounds nothing.  ``act="gelu_tanh"``:
+    ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))`` in the place of ``g * sigmoid(alpha * g)``."""
     _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
     n, inter = out.shape
     if gate_up.shape != (n, 2 * inter):
         raise KernelError("glu_bounded: gate_up must be [tokens, 2 * intermediate]")
     _call(_fn("elementwise", _elem(out), "erb_glu_bounded"), gate_up.data_ptr(), out.data_ptr(), n, inter, float(limit),
-          float(alpha), float(shift), _stream())
+          float(alpha), float(shift), GLU_ACTS[act], _stream())
 
 
 def softcap(logits: torch.Tensor, cap: float, dtype: torch.dtype) -> None:
@@ -472,10 +581,10 @@ def linear_glu_supported(a: torch.Tensor, weight: torch.Tensor, max_rows: int = 
     return a.shape[0] <= max_rows and weight.shape[0] % 2 == 0 and linear_few_rows_supported(a, weight, lda)
 
 
-def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bounded: tuple[float, float, float] | None = None) -> None:
+def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bounded: tuple | None = None) -> None:
     """out[M, N] = silu(a @ gate^T) * (a @ up^T) for ``weight = [gate; up]`` of shape [2N, K], in one
     launch; equal to ``linear`` into an [M, 2N] buffer followed by ``swiglu`` (each product is rounded
-    to bfloat16 before the gate).  ``bounded = (limit, alpha, shift)``: the gate of ``glu_bounded`` instead,
+    to bfloat16 before the gate).  ``bounded = (limit, alpha, shift[, act])``: the gate of ``glu_bounded`` instead,
     equal to ``linear`` followed by ``glu_bounded``."""
     _need(a, "a", torch.bfloat16, contiguous=False); _need(weight, "weight", torch.bfloat16)
     _need(out, "out", torch.bfloat16, contiguous=False)
@@ -486,9 +595,10 @@ def linear_glu(a: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, bounded
     lda = a.stride(0) if m > 1 else max(k, a.stride(0))
     ldo = out.stride(0) if m > 1 else max(n, out.stride(0))
     if bounded is not None:
-        limit, alpha, shift = bounded
+        limit, alpha, shift = bounded[:3]
+        act = bounded[3] if len(bounded) > 3 else "sigmoid"
         _call(_fn("gemm", "bfloat16", "erb_linear_skinny_glu_bounded"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
-              lda, k, ldo, float(limit), float(alpha), float(shift), _stream())
+              lda, k, ldo, float(limit), float(alpha), float(shift), GLU_ACTS[act], _stream())
         return
     _call(_fn("gemm", "bfloat16", "erb_linear_skinny_glu"), a.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k,
           lda, k, ldo, _stream())
@@ -821,8 +931,9 @@ DECODE_SPLIT_KEYS = 512
 
 def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                    seq_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
-                   scale: float, window: int = 0) -> None:
+                   scale: float, window: int = 0, keep_first: int = 0) -> None:
     """Causal attention of every token over its sequence's pages (general kernel, any portion sizes).
+    ``window`` > 0: a query sees the last ``window`` keys (its own included) and the first ``keep_first`` of the sequence.
 
     ``q``: ``[tokens, >= n_q_heads * D]`` view with unit inner stride (the q part of a qkv buffer);
     ``out``: ``[tokens, n_q_heads * D]``; pages ``[n_pages, n_kv_heads, page_size, D]``;
@@ -838,7 +949,7 @@ def attention_rows(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor
     _call(_fn("attention", _elem(q), "erb_attention_rows"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], seq_of_token.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), n, n_q_heads, nkv, d, page_size, int(window),
-          float(scale), _stream())
+          int(keep_first), float(scale), _stream())
 
 
 _sm_counts: dict[int, int] = {}
@@ -956,8 +1067,9 @@ def decode_scratch_floats(n_seqs: int, n_q_heads: int, head_dim: int, max_splits
 def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                      token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                      scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
-                     window: int = 0, split_keys: int = DECODE_SPLIT_KEYS) -> None:
+                     window: int = 0, split_keys: int = DECODE_SPLIT_KEYS, keep_first: int = 0) -> None:
     """Attention of one new token per sequence, keys cut into splits of ``split_keys`` (split-KV).
+    With a window the first ``keep_first`` keys stay visible; the first split of the window takes them along.
 
     ``token_of_seq`` int32 ``[sequences]`` gives each sequence's row in q/out/positions.  Scratch:
     ``part_acc`` float ``[sequences * heads * max_splits * D]``, ``part_ml`` twice
@@ -977,7 +1089,8 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
     _call(_fn("attention", _elem(q), "erb_attention_decode"), q.data_ptr(), q.stride(0), k_pages.data_ptr(),
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(),
-          max_splits, n_seqs, n_q_heads, nkv, d, page_size, int(window), int(split_keys), float(scale), _stream())
+          max_splits, n_seqs, n_q_heads, nkv, d, page_size, int(window), int(keep_first), int(split_keys), float(scale),
+          _stream())
 
 
 def decode_bulk_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,

@@ -7,6 +7,14 @@ serving query head ``h`` (edgerag/core/layers.py:117-134), scores scaled by ``he
 matrix ``[Wq; Wk; Wv]`` (row concatenation leaves every output column's arithmetic unchanged), so
 one product yields a row ``q heads | k heads | v heads`` per token.
 
+Options beyond the Llama decoder's, all constructor arguments: a ``window`` with ``keep_first`` (a query sees
+the last ``window`` keys and the first ``keep_first`` of its sequence, each at its true position), ``scale``,
+biases on q and k (``qk_bias``), a unit-RMS norm per head on q and k before the position encoding with one
+weight vector for all heads (``qk_norm_eps``), values that are the keys as projected, before norm and
+encoding (``values_are_keys``: no value projection; the cache still holds keys and values), and the tensors'
+names (``names``).  With any of bias, norm or shared values the step after the product is one kernel
+(``kernels.qk_prepare``) that also writes the cache.
+
 Single new tokens go through the split-KV decode kernel, portions of prompts through the row
 kernel; both read keys and values straight from the pages (no gather copy, unlike
 edgerag/cache/paged.py:208-238).
@@ -27,50 +35,87 @@ class Attention(Mixer):
 
     def __init__(self, hidden: int, n_q_heads: int, n_kv_heads: int, head_dim: int, position: PartSpec,
                  dtype: torch.dtype, device: torch.device, window: int = 0, own_kv: bool = True,
-                 scale: float | None = None) -> None:
+                 scale: float | None = None, keep_first: int = 0, qk_bias: bool = False, qk_norm_eps: float | None = None,
+                 values_are_keys: bool = False, names: dict[str, str] | None = None) -> None:
         if n_q_heads % n_kv_heads:
             raise ValueError(f"{n_q_heads} query heads are not divisible by {n_kv_heads} kv heads")
         self.hidden, self.n_q, self.n_kv, self.head_dim = hidden, n_q_heads, n_kv_heads, head_dim
         self.window = int(window or 0)
+        self.keep_first = int(keep_first or 0) if self.window > 0 else 0
+        self.qk_bias, self.qk_norm_eps, self.values_are_keys = bool(qk_bias), qk_norm_eps, bool(values_are_keys)
+        if (self.qk_bias or self.qk_norm_eps is not None or self.values_are_keys) and not own_kv:
+            raise ValueError("biases, head norms and shared values need the layer's own keys")
+        self.names = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
+                      "q_bias": "q_proj.bias", "k_bias": "k_proj.bias", "q_norm": "q_norm.weight", "k_norm": "k_norm.weight",
+                      **(names or {})}
+        self.q_bias = self.k_bias = self.q_norm = self.k_norm = None
         self.own_kv = own_kv
         self.scale = float(head_dim ** -0.5 if scale is None else scale)
         self.dtype, self.device = dtype, device
         self.position = build_part("position", position, dtype, device)
         self.q_width = n_q_heads * head_dim
         self.kv_width = n_kv_heads * head_dim
+        self.in_width = self.q_width + (1 if self.values_are_keys else 2) * self.kv_width
         self.w_qkv: torch.Tensor | None = None
         self.w_o: torch.Tensor | None = None
 
     def cache_spec(self) -> KVGroupSpec:
-        return KVGroupSpec(1, self.n_kv, self.head_dim, self.window)
+        return KVGroupSpec(1, self.n_kv, self.head_dim, self.window, keep_first=self.keep_first)
 
     def weight_specs(self) -> list[WeightSpec]:
-        specs = [WeightSpec("q_proj.weight", (self.q_width, self.hidden))]
+        nm = self.names
+        specs = [WeightSpec(nm["q"], (self.q_width, self.hidden))]
         if self.own_kv:
-            specs += [WeightSpec("k_proj.weight", (self.kv_width, self.hidden)),
-                      WeightSpec("v_proj.weight", (self.kv_width, self.hidden))]
-        return specs + [WeightSpec("o_proj.weight", (self.hidden, self.q_width))]
+            specs.append(WeightSpec(nm["k"], (self.kv_width, self.hidden)))
+            if not self.values_are_keys:
+                specs.append(WeightSpec(nm["v"], (self.kv_width, self.hidden)))
+        if self.qk_bias:
+            specs += [WeightSpec(nm["q_bias"], (self.q_width,), "vector32"), WeightSpec(nm["k_bias"], (self.kv_width,), "vector32")]
+        if self.qk_norm_eps is not None:
+            specs += [WeightSpec(nm["q_norm"], (self.head_dim,), "vector32"), WeightSpec(nm["k_norm"], (self.head_dim,), "vector32")]
+        return specs + [WeightSpec(nm["o"], (self.hidden, self.q_width))]
 
     def load_weights(self, tensors: dict[str, torch.Tensor]) -> None:
+        nm = self.names
+        f32 = lambda t: t.to(device=self.device, dtype=torch.float32).contiguous()   # noqa: E731
         if self.own_kv:
-            parts = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+            parts = [tensors[nm["q"]], tensors[nm["k"]]] + ([] if self.values_are_keys else [tensors[nm["v"]]])
         else:  # rows for k and v stay zero: the layer reads another layer's cache
             pad = torch.zeros((2 * self.kv_width, self.hidden), dtype=self.dtype, device=self.device)
-            parts = [tensors["q_proj.weight"], pad]
+            parts = [tensors[nm["q"]], pad]
         self.w_qkv = torch.cat([p.to(device=self.device, dtype=self.dtype) for p in parts], dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].to(device=self.device, dtype=self.dtype).contiguous()
+        self.w_o = tensors[nm["o"]].to(device=self.device, dtype=self.dtype).contiguous()
+        if self.qk_bias:
+            self.q_bias, self.k_bias = f32(tensors[nm["q_bias"]]), f32(tensors[nm["k_bias"]])
+        if self.qk_norm_eps is not None:
+            self.q_norm, self.k_norm = f32(tensors[nm["q_norm"]]), f32(tensors[nm["k_norm"]])
+
+    def _prepare(self, x, qkv, ctx, pages, slots) -> None:
+        """The input product and everything between it and the attention: biases, head norms, positions, cache write."""
+        d = self.head_dim
+        if self.qk_bias or self.qk_norm_eps is not None or self.values_are_keys:
+            pos = self.position
+            kernels.linear(x, self.w_qkv, qkv)
+            kernels.qk_prepare(qkv, ctx.positions, self.n_q, self.n_kv, d, q_bias=self.q_bias, k_bias=self.k_bias,
+                               q_norm=self.q_norm, k_norm=self.k_norm, eps=self.qk_norm_eps or 0.0,
+                               inv_freq=getattr(pos, "inv_freq", None), rot_dim=getattr(pos, "rot_dim", 0),
+                               pairs=bool(getattr(pos, "pairs", False)), values_are_keys=self.values_are_keys, slots=slots,
+                               k_pages=None if pages is None else pages[0], v_pages=None if pages is None else pages[1],
+                               page_size=ctx.page_size)
+            return
+        if not self.position.project_apply_store(x, self.w_qkv, qkv, ctx, self.n_q, self.n_kv, d, pages, slots):
+            kernels.linear(x, self.w_qkv, qkv)
+            self.position.apply_and_store(qkv, ctx, self.n_q, self.n_kv, d, pages, slots)
 
     def forward(self, x: torch.Tensor, ctx, call: LayerCall) -> torch.Tensor:
         n = x.shape[0]
         d = self.head_dim
-        qkv = ctx.buf("attn.qkv", (n, self.q_width + 2 * self.kv_width), self.dtype)
+        qkv = ctx.buf("attn.qkv", (n, self.in_width), self.dtype)
         k_pages, v_pages = ctx.pages_of(call.cache_layer)
         group = ctx.group_of(call.cache_layer)
         write = call.writes_cache and self.own_kv
         pages, slots = ((k_pages, v_pages), ctx.slots[group]) if write else (None, None)
-        if not self.position.project_apply_store(x, self.w_qkv, qkv, ctx, self.n_q, self.n_kv, d, pages, slots):
-            kernels.linear(x, self.w_qkv, qkv)
-            self.position.apply_and_store(qkv, ctx, self.n_q, self.n_kv, d, pages, slots)
+        self._prepare(x, qkv, ctx, pages, slots)
         out = ctx.buf("attn.out", (n, self.q_width), self.dtype)
         tables = ctx.block_tables[group]
         nd = ctx.n_decode
@@ -98,7 +143,7 @@ class Attention(Mixer):
             else:
                 kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                          out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits,
-                                         window=self.window, split_keys=split)
+                                         window=self.window, split_keys=split, keep_first=self.keep_first)
         if n > nd and kernels.prefill_tc_supported(self.dtype, d, self.window, ctx.page_size):
             blocks = kernels.prefill_tc_blocks(ctx.host_q_len[nd:])
             # a portion that is short against its past: its few blocks' keys are cut into ranges
@@ -113,7 +158,7 @@ class Attention(Mixer):
                                          part_ml=part_ml)
         elif n > nd:
             kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:],
-                                   out[nd:], self.n_q, self.scale, window=self.window)
+                                   out[nd:], self.n_q, self.scale, window=self.window, keep_first=self.keep_first)
         n_parts = kernels.linear_parts_count(out, self.w_o)
         if n_parts:      # the rows of a larger decode step: k split over the SMs, the norm after adds the parts
             y = ctx.buf("mixer.out_parts", (n_parts, n, self.hidden), torch.float32)

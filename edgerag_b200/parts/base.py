@@ -16,7 +16,10 @@ Interfaces (duck-typed; the base classes document them):
   write in one kernel, where the part has one);
 * ``Mixer.cache_spec()`` and ``Mixer.forward(x, ctx, call) -> Tensor``;
 * ``FeedForward.forward(x, ctx) -> Tensor``;
-* ``Block.forward(hidden, delta, ctx, call) -> delta`` (the update that is still to be added).
+* ``Block.forward(hidden, delta, ctx, call) -> delta`` (the update that is still to be added: rows, float32
+  partial sums, or a ``NormedUpdate`` when a norm has to act on it before the add);
+* ``StreamOp.begin(ctx, hidden)`` and ``StreamOp.forward(hidden, delta, ctx, call) -> delta``: a step of the run
+  order between layers that rewrites the residual stream itself (``StreamCall`` in the plan's schedule).
 """
 
 from __future__ import annotations
@@ -82,15 +85,36 @@ class LayerCall:
     writes_cache: bool = True
 
 
+@dataclass(frozen=True)
+class StreamCall:
+    """An entry of the run order that is no layer: stream operation ``op`` of the plan runs, told which of its
+    uses this is (``index``: e.g. the number of the pass a loop over layers is about to start)."""
+
+    op: int
+    index: int = 0
+
+
+@dataclass
+class NormedUpdate:
+    """An update of the residual stream on which a norm has still to act before it is added:
+    ``hidden += norm(tensor)``.  A block whose sublayers end in a norm hands this on as its ``delta``, so that
+    the norm, the add and the next norm can be one kernel."""
+
+    tensor: torch.Tensor
+    norm: "Norm"
+
+
 @dataclass
 class ModelPlan:
     hidden_size: int
     vocab_size: int
     embedding: PartSpec
     layers: list[LayerSpec]
-    schedule: list[LayerCall]
+    schedule: list["LayerCall | StreamCall"]
     final_norm: PartSpec | None
     head: PartSpec
+    #: operations on the stream that the schedule's ``StreamCall`` entries name by index
+    stream_ops: list[PartSpec] = field(default_factory=list)
     #: prefixes under which a checkpoint may store the model-relative names, tried in order
     name_prefixes: tuple[str, ...] = ("model.text_model.", "model.", "")
     #: tensors of the checkpoint that belong to other towers and are not an error
@@ -121,8 +145,15 @@ class Norm(Part):
         ``write_back``; ``out`` receives the normed rows (all rows, or ``rows`` of them).  ``delta`` is
         ``[rows, hidden]`` of the model's element type or float32 partial sums ``[parts, rows, hidden]``.  ``settled`` is a
         hint that a norm may ignore: the caller vouches that ``hidden`` was not written by the kernel
-        launched just before this call (only ``delta`` was), so it may be read while that kernel runs."""
+        launched just before this call (only ``delta`` was), so it may be read while that kernel runs.
+        ``delta`` may also be a ``NormedUpdate``; a norm without a kernel for that calls ``settle_update``
+        first and goes on without an update."""
         raise NotImplementedError
+
+    def add_normed(self, hidden: torch.Tensor, x: torch.Tensor) -> None:
+        """``hidden += self(x)``: this norm applied to the rows (or partial sums) ``x``, the result kept in
+        float32 and added to the stream.  Norms that may close a sublayer implement it."""
+        raise NotImplementedError(f"{type(self).__name__} cannot close a sublayer")
 
 
 class PositionEncoding(Part):
@@ -163,13 +194,38 @@ class FeedForward(Part):
 
 
 class Block(Part):
-    def forward(self, hidden: torch.Tensor, delta: torch.Tensor | None, ctx: Any, call: LayerCall) -> torch.Tensor | None:
+    def forward(self, hidden: torch.Tensor, delta: "torch.Tensor | NormedUpdate | None", ctx: Any,
+                call: LayerCall) -> "torch.Tensor | NormedUpdate | None":
         raise NotImplementedError
+
+
+class StreamOp(Part):
+    """A step between layers that rewrites the residual stream (not an update of it)."""
+
+    def begin(self, ctx: Any, hidden: torch.Tensor) -> None:
+        """Called once per step right after the embedding has written ``hidden`` (to keep what the
+        operation needs of it later)."""
+
+    def forward(self, hidden: torch.Tensor, delta: "torch.Tensor | NormedUpdate | None", ctx: Any,
+                call: StreamCall) -> "torch.Tensor | NormedUpdate | None":
+        """Add the pending ``delta``, rewrite ``hidden`` in place, return what is still to be added (usually None)."""
+        raise NotImplementedError
+
+
+def settle_update(hidden: torch.Tensor, delta: "torch.Tensor | NormedUpdate | None", dtype: torch.dtype) -> None:
+    """``hidden +=`` the pending update, whatever its form (rows, float32 partial sums, an update to be normed)."""
+    from ..ops import kernels
+    if delta is None:
+        return
+    if isinstance(delta, NormedUpdate):
+        delta.norm.add_normed(hidden, delta.tensor)
+    else:
+        kernels.residual_add(hidden, delta, dtype)
 
 
 # --- registries -------------------------------------------------------------------------------
 
-CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head")
+CATEGORIES = ("norm", "position", "mixer", "ffn", "block", "embedding", "head", "stream")
 _REGISTRY: dict[str, dict[str, Callable[..., Part]]] = {c: {} for c in CATEGORIES}
 
 

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from ..ops import kernels
-from .base import Norm, WeightSpec, register_part
+from .base import Norm, NormedUpdate, WeightSpec, register_part, settle_update
 
 
 @register_part("norm", "rmsnorm")
@@ -40,5 +40,10 @@ class RMSNorm(Norm):
         self.weight = (w + self.weight_offset if self.weight_offset else w).contiguous()
 
     def forward(self, hidden, out, delta=None, rows=None, write_back=True, settled=False) -> None:
+        if isinstance(delta, NormedUpdate):        # closed by its own norm and added first (no fused kernel for that here)
+            if rows is not None or not write_back:
+                raise ValueError("a pending update that a norm has to close can only be added to all rows")
+            settle_update(hidden, delta, self.dtype)
+            delta, settled = None, False
         kernels.add_rmsnorm(hidden, self.weight, out, self.eps, delta=delta, rows=rows, write_back=write_back, settled=settled,
                             exact=self.exact)

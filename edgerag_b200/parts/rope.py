@@ -6,6 +6,10 @@
 the same kernel that writes keys and values to their cache slots, so the cache holds rotated keys
 (edgerag/core/layers.py:301-306) and a key's encoding depends on its own logical position only.
 
+``RotaryPairs`` turns neighbouring pairs ``(2i, 2i + 1)`` of the first ``rot_dim`` entries of a head by
+``position * theta**(-2i / rot_dim) / factor`` (``factor``: linear scaling of positions) and leaves the rest
+of the head as it is.
+
 ``NoPosition`` encodes nothing and only writes the cache; it is what a mixer uses when another
 part has already put positions into the stream.
 """
@@ -21,6 +25,7 @@ from .base import PositionEncoding, register_part
 @register_part("position", "rope_halves")
 class RotaryHalves(PositionEncoding):
     graph_safe = True
+    pairs = False            # which entries make a pair: (i, i + rot_dim / 2)
 
     def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device,
                  rot_dim: int | None = None) -> None:
@@ -47,9 +52,36 @@ class RotaryHalves(PositionEncoding):
         return True
 
 
+@register_part("position", "rope_pairs")
+class RotaryPairs(PositionEncoding):
+    graph_safe = True
+    pairs = True             # (2i, 2i + 1)
+
+    def __init__(self, head_dim: int, theta: float, dtype: torch.dtype, device: torch.device, rot_dim: int | None = None,
+                 factor: float = 1.0) -> None:
+        self.head_dim = head_dim
+        self.rot_dim = head_dim if rot_dim is None else int(rot_dim)
+        if self.rot_dim % 2 or not 0 <= self.rot_dim <= head_dim:
+            raise ValueError(f"rot_dim {self.rot_dim} must be even and at most head_dim {head_dim}")
+        if not factor > 0:
+            raise ValueError(f"scaling factor {factor} must be positive")
+        self.theta, self.factor = float(theta), float(factor)
+        i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+        inv_freq = self.theta ** (-2.0 * i / max(self.rot_dim, 1)) / self.factor
+        self.inv_freq = inv_freq.to(device=device, dtype=torch.float32).contiguous()
+
+    def apply_and_store(self, qkv, ctx, n_q_heads, n_kv_heads, head_dim, pages, slots) -> None:
+        k_pages, v_pages = pages if pages is not None else (None, None)
+        kernels.qk_prepare(qkv, ctx.positions, n_q_heads, n_kv_heads, head_dim, inv_freq=self.inv_freq, rot_dim=self.rot_dim,
+                           pairs=True, slots=slots, k_pages=k_pages, v_pages=v_pages, page_size=ctx.page_size)
+
+
 @register_part("position", "none")
 class NoPosition(PositionEncoding):
     graph_safe = True
+    pairs = False
+    rot_dim = 0
+    inv_freq = None
 
     def __init__(self, dtype: torch.dtype, device: torch.device, **_unused) -> None:
         pass
