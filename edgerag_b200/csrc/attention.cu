@@ -1,7 +1,7 @@
 // Causal grouped-query attention over cache pages, for any element type and head size.
 //
 // These are the general kernels: CUDA-core arithmetic in float, any head size that is a multiple
-// of 16 up to 256, any page size, any number of heads and groups, an optional window.  They serve
+// of 8 up to 128 or of 16 up to 256, any page size, any number of heads and groups, an optional window.  They serve
 // the 32-bit path and every shape the tensor-core kernels do not take.
 //
 // Cache layout (one layer): pages[page][kv head][offset][D]; a token at logical position p of a
@@ -322,8 +322,8 @@ int launch_decode(const void* q, int q_row_stride, const void* k_pages, const vo
 
 int check_common(const char* who, int nq, int nkv, int head_dim, int page_size, int max_pages) {
   if (nq <= 0 || nkv <= 0 || nq % nkv) return fail(ERB_ERR_ARG, "%s: %d query heads / %d kv heads", who, nq, nkv);
-  if (head_dim < 16 || head_dim > 256 || head_dim % 16)
-    return fail(ERB_ERR_UNSUPPORTED, "%s: head_dim %d is not a multiple of 16 in [16, 256]", who, head_dim);
+  if (head_dim < 8 || head_dim > 256 || (head_dim <= 128 ? head_dim % 8 : head_dim % 16))
+    return fail(ERB_ERR_UNSUPPORTED, "%s: head_dim %d is not a multiple of 8 up to 128 or of 16 up to 256", who, head_dim);
   if (page_size <= 0 || max_pages <= 0) return fail(ERB_ERR_ARG, "%s: bad page_size/max_pages", who);
   return ERB_OK;
 }
@@ -332,6 +332,10 @@ int check_common(const char* who, int nq, int nkv, int head_dim, int page_size, 
 
 #define ERB_DISPATCH_D(FN, ...)                                                                \
   switch (head_dim) {                                                                          \
+    case 8: return FN<elem_t, 8>(__VA_ARGS__);     case 24: return FN<elem_t, 24>(__VA_ARGS__);   \
+    case 40: return FN<elem_t, 40>(__VA_ARGS__);   case 56: return FN<elem_t, 56>(__VA_ARGS__);   \
+    case 72: return FN<elem_t, 72>(__VA_ARGS__);   case 88: return FN<elem_t, 88>(__VA_ARGS__);   \
+    case 104: return FN<elem_t, 104>(__VA_ARGS__); case 120: return FN<elem_t, 120>(__VA_ARGS__); \
     case 16: return FN<elem_t, 16>(__VA_ARGS__);   case 32: return FN<elem_t, 32>(__VA_ARGS__);   \
     case 48: return FN<elem_t, 48>(__VA_ARGS__);   case 64: return FN<elem_t, 64>(__VA_ARGS__);   \
     case 80: return FN<elem_t, 80>(__VA_ARGS__);   case 96: return FN<elem_t, 96>(__VA_ARGS__);   \

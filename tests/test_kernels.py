@@ -813,11 +813,11 @@ def test_decode_attention_finds_far_keys_and_follows_rising_maxima(k, which, nq,
 def test_attention_refuses_bad_head_sizes(k):
     from edgerag_b200.ops.kernels import KernelError
 
-    q = torch.zeros((1, 2 * 24), device="cuda")
-    kp = torch.zeros((1, 2, 4, 24), device="cuda")
+    q = torch.zeros((1, 2 * 20), device="cuda")
+    kp = torch.zeros((1, 2, 4, 20), device="cuda")
     t = torch.zeros((1, 1), dtype=torch.int32, device="cuda")
     z = torch.zeros(1, dtype=torch.int32, device="cuda")
-    with pytest.raises(KernelError, match="head_dim 24"):
+    with pytest.raises(KernelError, match="head_dim 20"):
         k.attention_rows(q, kp, kp, t, z, z, torch.empty_like(q), 2, 1.0)
 
 
