@@ -24,6 +24,9 @@
 // that it has become far too low (P is a floating-point number: a reference that is low by twenty powers
 // of two costs no precision).  So most tiles need no search for a maximum and no rescaling of O.
 //
+// With a window (and a count of first keys that stay visible whatever the distance) a block walks only the
+// key tiles that hold keys some row of it sees; pages of such a tile that hold none are not brought.
+//
 // A portion that is short against its past (512 new tokens after 7,000 cached ones) gives few blocks,
 // each with a long walk over the keys.  The launch may then cut every block's key tiles into
 // `key_splits` ranges, one block per range (blockIdx.z): a block leaves its rows' unnormalised O, reference
@@ -32,6 +35,7 @@
 // Every wait is bounded: a thread that gives up raises a block-wide flag, every other wait of the
 // block then ends too, the block records a code in *status, lets its copies land, frees its TMEM
 // and returns.
+#include <limits.h>
 #include <stdarg.h>
 #include <stdio.h>
 
@@ -77,7 +81,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
                          const int* __restrict__ block_tables, int max_pages, const int* __restrict__ seq_starts,
                          const int* __restrict__ positions, __nv_bfloat16* __restrict__ out, int out_row_stride,
                          int n_seqs, int nq, int nkv, int page_size, float scale_log2, int* __restrict__ status,
-                         int key_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                         int key_splits, float* __restrict__ part_o, float* __restrict__ part_ml, int window, int keep_first) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;             // the swizzle repeats every 1024 bytes
@@ -129,11 +133,19 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   const int pos0 = positions[q0];                       // position of the block's first row
   const int last_key = pos0 + rows - 1;                 // the last key any row of the block sees
   const int rows_t[2] = {min(rows, BM), max(rows - BM, 0)};
-  // key tiles each query tile walks: up to the tile that holds its last row's own key
-  const int n_t[2] = {(pos0 + rows_t[0] - 1) / BN + 1, rows_t[1] > 0 ? last_key / BN + 1 : 0};
+  // With a window a row sees the keys of the last `window` positions (its own included) and the first
+  // `keep_first` keys of its sequence.  The block then walks the tiles that hold kept keys and lie before
+  // its first row's window, and after them the tiles from that window's first key on: walk step i is key
+  // tile i for i < n_kept and key tile i + skip from there.  Without a window the walk is the tiles themselves.
+  const int lo_block = window > 0 ? max(pos0 - window + 1, 0) : 0;
+  const int n_kept = window > 0 ? min((keep_first + BN - 1) / BN, lo_block / BN) : 0;
+  const int skip = lo_block / BN - n_kept;
+  auto tile_of = [&](int i) { return i < n_kept ? i : i + skip; };
+  // steps each query tile walks: up to the tile that holds its last row's own key
+  const int n_t[2] = {(pos0 + rows_t[0] - 1) / BN + 1 - skip, rows_t[1] > 0 ? last_key / BN + 1 - skip : 0};
   const int n_kv = max(n_t[0], n_t[1]);
   // The last key tile holds `valid_last` keys; the second product stops at the 16 keys that hold the last one.
-  const int valid_last = last_key - (n_kv - 1) * BN + 1;
+  const int valid_last = last_key - (n_kv - 1 + skip) * BN + 1;
   const int ksteps_last = (valid_last + 15) >> 4;
   // This block's range of key tiles [j0, j1) (all of them without splits), and where each query tile stops in it.
   const int per_split = (n_kv + key_splits - 1) / key_splits;
@@ -173,12 +185,24 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     };
     // The page a lane brings is read from the block table one tile ahead, so that the latency of that
     // load is not in the way of the copies.
+    // A page is brought if some row of the block sees one of its keys: no key behind the block's last one,
+    // and with a window a key from the first row's window on or a kept one.  (Pages that the window has left
+    // behind may have been given back to the pool: their entries of the block table are not read.)
     auto page_of = [&](int j) {
-      const int first_key = j * BN + lane * page_size;
-      return (j < n_kv && lane < pages_per_tile && first_key <= last_key) ? bt[first_key / page_size] : -1;
+      const int first_key = tile_of(j) * BN + lane * page_size;
+      const bool seen = window <= 0 || first_key + page_size > lo_block || first_key < keep_first;
+      return (j < n_kv && lane < pages_per_tile && first_key <= last_key && seen) ? bt[first_key / page_size] : -1;
     };
-    auto bring = [&](int j, int page, const CUtensorMap* map, uint32_t dst, uint32_t full) {
-      const int n_pages = min(pages_per_tile, (last_key - j * BN) / page_size + 1);
+    auto bring = [&](int j, int page, const CUtensorMap* map, uint32_t dst, uint32_t full, bool zero_rest) {
+      const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
+      if (zero_rest && window > 0 && page < 0 && lane < pages_per_tile && tile_of(j) * BN + lane * page_size <= last_key) {
+        // the rows of a page that is not brought: nobody sees them (their P is zero), but whatever an earlier
+        // tile left there would spoil 0 * x of the second product if it were no number
+        uint4* rows_of_page = reinterpret_cast<uint4*>(smem + (dst - base) + (uint32_t)lane * page_bytes);
+        for (uint32_t i = 0; i < page_bytes / 16; ++i) rows_of_page[i] = make_uint4(0, 0, 0, 0);
+        fence_async_proxy();
+      }
+      __syncwarp();
       if (lane == 0) mbar_expect(full, (uint32_t)n_pages * page_bytes);
       __syncwarp();
       if (page >= 0) tma_load_rows(dst + (uint32_t)lane * page_bytes, map, (page * nkv + kvh) * page_size, full);
@@ -191,11 +215,11 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       page_next = page_of(j + 1);
       if (jj >= kKStages) ok = wait(kBarKEmpty + ks, ((jj / kKStages) - 1) & 1);
       if (!ok) break;
-      bring(j, page, &map_k, sK + ks * kKvBytes, bar(kBarKFull + ks));
+      bring(j, page, &map_k, sK + ks * kKvBytes, bar(kBarKFull + ks), false);
       copies_k = jj + 1;
       if (jj >= kVStages) ok = wait(kBarVEmpty + vs, ((jj / kVStages) - 1) & 1);
       if (!ok) break;
-      bring(j, page, &map_v, sV + vs * kKvBytes, bar(kBarVFull + vs));
+      bring(j, page, &map_v, sV + vs * kKvBytes, bar(kBarVFull + vs), true);
       copies_v = jj + 1;
     }
   } else if (warp == kIssueWarp) {
@@ -283,12 +307,15 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       ok = __all_sync(0xffffffffu, ok) != 0;             // the same answer for every lane: TMEM loads are collective
     };
     float m_ref = -INFINITY, l_run = 0.f;                // l_run: this thread's half of the row's sum
+    const int win_lo = window > 0 ? my_pos - window + 1 : INT_MIN;      // first key of this row's window
+    auto hidden = [&](int key) { return key > my_pos || (key < win_lo && key >= keep_first); };
     for (int j = j0; j < n_end[t]; ++j) {
       wait(kBarSFull + t, (j - j0) & 1);
       if (!ok) break;
       fence_after_sync();
-      const int key0 = j * BN + half * 64;
-      const bool diagonal = j * BN + BN - 1 > pos0 + t * BM;             // some row of the tile has masked keys here
+      const int tile_key0 = tile_of(j) * BN, key0 = tile_key0 + half * 64;
+      // some row of the query tile has hidden keys here: keys after its own, or keys before its window that are not kept
+      const bool diagonal = tile_key0 + BN - 1 > pos0 + t * BM || (window > 0 && tile_key0 < pos0 + t * BM + BM - window);
       // The exponentials are taken against the reference maximum of the tiles before, without looking
       // for this tile's maximum first: P is a floating-point number, so a reference that is too low by
       // many powers of two costs no precision.  Only when a row's sum shows that the reference is far
@@ -306,7 +333,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
             tmem_ld32(t_s + 32 * c, s);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) m_half = fmaxf(m_half, (diagonal && key0 + 32 * c + i > my_pos) ? -INFINITY : s[i]);
+            for (int i = 0; i < 32; ++i) m_half = fmaxf(m_half, (diagonal && hidden(key0 + 32 * c + i)) ? -INFINITY : s[i]);
           }
           *mine = m_half;
           named_barrier(pair_barrier, 64);
@@ -346,7 +373,7 @@ attention_prefill_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
           if (diagonal) {
 #pragma unroll
             for (int i = 0; i < 16; ++i)
-              if (key0 + 16 * c + i > my_pos) sc[i] = -INFINITY;
+              if (hidden(key0 + 16 * c + i)) sc[i] = -INFINITY;
           }
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
@@ -472,8 +499,8 @@ ERB_EXPORT int erb_attention_prefill_tc_supported(int head_dim, int page_size) {
   return head_dim == HD && page_size >= 8 && page_size <= BN && (page_size & (page_size - 1)) == 0;
 }
 
-// Portions of prompts only (bfloat16, head_dim 64, no window, pages of 8 to 128 tokens, a power of
-// two).  q / out: row t is token t of the batch; seq_starts: int32 [n_seqs + 1] token offsets of the
+// Portions of prompts only (bfloat16, head_dim 64, pages of 8 to 128 tokens, a power of two).  window > 0:
+// a row sees its last `window` keys (its own included) and the first `keep_first` keys of its sequence.  q / out: row t is token t of the batch; seq_starts: int32 [n_seqs + 1] token offsets of the
 // sequences to process (consecutive rows of block_tables); n_blocks: sum over them of
 // ceil(length / 256) (an upper bound is fine); n_pool_pages: pages of k_pages / v_pages (the tensor
 // maps cover the whole pool).  status: device int, set non-zero if a block gave up waiting.
@@ -486,7 +513,7 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
                                         const int* seq_starts, const int* positions, void* out, int out_row_stride,
                                         int n_seqs, int n_blocks, int nq, int nkv, int head_dim, int page_size,
                                         float scale, int* status, int key_splits, int first_row, int n_rows,
-                                        float* part_o, float* part_ml, void* stream) {
+                                        float* part_o, float* part_ml, int window, int keep_first, void* stream) {
   if (n_seqs <= 0 || n_blocks <= 0) return ERB_OK;
   if (key_splits < 1 || key_splits > 64 || (key_splits > 1 && (!part_o || !part_ml || first_row < 0 || n_rows <= 0 || ((uintptr_t)part_o & 15))))
     return fail(ERB_ERR_ARG, "attention_prefill_tc: bad split arguments");
@@ -516,7 +543,8 @@ ERB_EXPORT int erb_attention_prefill_tc(const void* q, int q_row_stride, const v
   const float scale_log2 = scale * 1.4426950408889634f;
   launch_chained(attention_prefill_kernel, dim3(nq, n_blocks, key_splits), dim3(kThreads), kSmemBytes, (cudaStream_t)stream, mk, mv,
                  (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, seq_starts, positions,
-                 (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv, page_size, scale_log2, status, key_splits, part_o, part_ml);
+                 (__nv_bfloat16*)out, out_row_stride, n_seqs, nq, nkv, page_size, scale_log2, status, key_splits, part_o, part_ml,
+                 window > 0 ? window : 0, window > 0 && keep_first > 0 ? keep_first : 0);
   if ((rc = check_launch("attention_prefill_tc")) || key_splits == 1) return rc;
   launch_chained(attention_prefill_merge_kernel, dim3((n_rows * nq + 3) / 4), dim3(128), 0, (cudaStream_t)stream, part_o, part_ml,
                  (__nv_bfloat16*)out, out_row_stride, first_row, n_rows, nq, key_splits);

@@ -125,7 +125,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
                              float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                              int nkv, int page_size, int split_keys, float scale_log2, int hg,
                              __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status,
-                             int* __restrict__ counters) {
+                             int* __restrict__ counters, int window, int keep_first) {
   // Everything up to chain_wait() below reads only what earlier steps or the host wrote (the batch's
   // metadata, keys and values of earlier tokens), so it runs while the kernel before this one (the
   // one that rotates q and writes this step's keys and values) is still at work.
@@ -158,11 +158,25 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   const bool serves = hh < hg_here;
   const int t = token_of_seq[seq];
   const int pos = positions[t];
-  const int begin = split * split_keys;
-  const int end = min(pos + 1, begin + split_keys);
+  // With a window the token sees the keys from k_lo on and the first keep_first keys.  Splits stay at absolute
+  // multiples of split_keys and are counted from the one that holds k_lo.  With several heads per block whole
+  // pages are copied, so the first split starts at the page of k_lo and the keys before k_lo are passed over.
+  // The first split also walks, before its own keys, the kept keys that lie before everything the splits read
+  // (pages the window has left behind, other than those of kept keys, may have been given back: they are not touched).
+  const int k_lo = window > 0 ? max(pos - window + 1, 0) : 0;
+  const int first_split = k_lo / split_keys;
+  const int k_first = hg == 1 ? k_lo : (k_lo / page_size) * page_size;
+  const int begin = max((first_split + split) * split_keys, k_first);
+  const int end = min(pos + 1, (first_split + split + 1) * split_keys);
   if (begin >= end) return;
   const int* bt = block_tables + (size_t)seq * max_pages;
-  const int n_tiles = (end - begin + STAGE_KEYS - 1) / STAGE_KEYS;
+  const int kept = (window > 0 && split == 0) ? min(keep_first, k_first) : 0;
+  const int kept_tiles = (kept + STAGE_KEYS - 1) / STAGE_KEYS;
+  const int n_tiles = kept_tiles + (end - begin + STAGE_KEYS - 1) / STAGE_KEYS;
+  auto tile_begin = [&](int tile) { return tile < kept_tiles ? tile * STAGE_KEYS : begin + (tile - kept_tiles) * STAGE_KEYS; };
+  auto tile_end = [&](int tile) {
+    return tile < kept_tiles ? min(kept, (tile + 1) * STAGE_KEYS) : min(end, begin + (tile - kept_tiles + 1) * STAGE_KEYS);
+  };
 
   if (tid == 0) {
 #pragma unroll
@@ -174,18 +188,21 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   const int first_page = begin / page_size;
   const int n_pages = (end - 1) / page_size - first_page + 1;
   for (int i = tid; i < n_pages; i += kDecThreads) s_pages[i] = bt[first_page + i];
+  int* s_kept = s_pages + split_keys / page_size + 2;     // the pages of the kept keys
+  for (int i = tid; i * page_size < kept; i += kDecThreads) s_kept[i] = bt[i];
   __syncthreads();
 
   auto issue = [&](int tile) {   // thread 0 only
     const int s = tile % kStages;
-    const int kb = begin + tile * STAGE_KEYS, ke = min(end, kb + STAGE_KEYS);
+    const int kb = tile_begin(tile), ke = tile_end(tile);
+    const int* pages_of_tile = tile < kept_tiles ? s_kept : s_pages - first_page;
     const uint32_t bar = sBar + 8 * s;
     if (hg == 1) {
       // one head: copy exactly the visible keys, one run per page
       mbar_expect(bar, (uint32_t)(ke - kb) * ROW * 2);
       int k = kb;
       while (k < ke) {
-        const int page = s_pages[k / page_size - first_page], off = k % page_size;
+        const int page = pages_of_tile[k / page_size], off = k % page_size;
         const int n = min(page_size - off, ke - k);
         const size_t src = (((size_t)page * nkv + kvh0) * page_size + off) * D;
         const uint32_t dst = (uint32_t)(s * STAGE_BYTES + (k - kb) * ROW);
@@ -200,7 +217,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
       const uint32_t chunk_bytes = (uint32_t)(hg_here * page_size) * ROW;   // what one page brings
       mbar_expect(bar, (uint32_t)n_pg * chunk_bytes * 2);
       for (int j = 0; j < n_pg; ++j) {
-        const int page = s_pages[kb / page_size + j - first_page];
+        const int page = pages_of_tile[kb / page_size + j];
         const size_t src = ((size_t)page * nkv + kvh0) * page_size * D;
         const uint32_t dst = (uint32_t)(s * STAGE_BYTES) + (uint32_t)j * slot_bytes;
         bulk_copy(sK + dst, k_pages + src, chunk_bytes, bar);
@@ -212,7 +229,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   const int old_end = (pos / page_size) * page_size;
   int issued = 0;
   if (tid == 0) {
-    while (issued < kStages && issued < n_tiles && min(end, begin + (issued + 1) * STAGE_KEYS) <= old_end) issue(issued++);
+    while (issued < kStages && issued < n_tiles && tile_end(issued) <= old_end) issue(issued++);
   }
   chain_wait();
   if (tid == 0) {
@@ -249,8 +266,13 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   for (int tile = 0; tile < n_tiles; ++tile) {
     const int s = tile % kStages;
     if (ok && !mbar_wait(sBar + 8 * s, (tile / kStages) & 1)) ok = false;
-    const int n_here = min(end - (begin + tile * STAGE_KEYS), STAGE_KEYS);
+    const int n_here = tile_end(tile) - tile_begin(tile);
     if (ok && serves && key_in_stage < n_here) {
+      // keys of the first page that lie before the window and are not kept (only where whole pages are copied)
+      const int key0 = tile_begin(tile) + key_in_stage;
+      bool hidden[kKeysPerGroup];
+#pragma unroll
+      for (int u = 0; u < kKeysPerGroup; ++u) hidden[u] = key_in_stage + u >= n_here || (key0 + u < k_lo && key0 + u >= keep_first);
       const uint8_t* kt = smem + s * STAGE_BYTES + row_offset + chunk * 16;
       const uint8_t* vt = kt + kStages * STAGE_BYTES;
       uint4 kraw[kKeysPerGroup];
@@ -286,14 +308,15 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
         float m_new = m_run[g];
 #pragma unroll
         for (int u = 0; u < kKeysPerGroup; ++u) {
-          if (key_in_stage + u >= n_here) sc[g][u] = -INFINITY;     // keys past the end of the split
+          if (hidden[u]) sc[g][u] = -INFINITY;     // keys past the end of the split or before the window
           m_new = fmaxf(m_new, sc[g][u]);
         }
-        // key_in_stage < n_here: at least one key is real, so m_new is finite
-        const float a = exp2f(m_run[g] - m_new);
+        // (all of the group's keys may be hidden so far: exponentials are then taken against 0 and are 0)
+        const float m_ref = m_new == -INFINITY ? 0.f : m_new;
+        const float a = exp2f(m_run[g] - m_ref);
         float sum = 0.f;
 #pragma unroll
-        for (int u = 0; u < kKeysPerGroup; ++u) { p[g][u] = exp2f(sc[g][u] - m_new); sum += p[g][u]; }
+        for (int u = 0; u < kKeysPerGroup; ++u) { p[g][u] = exp2f(sc[g][u] - m_ref); sum += p[g][u]; }
         l_run[g] = l_run[g] * a + sum;
         m_run[g] = m_new;
 #pragma unroll
@@ -303,7 +326,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
       for (int u = 0; u < kKeysPerGroup; ++u) {
         float vf[8];
         unpack8(vraw[u], vf);
-        if (key_in_stage + u >= n_here) {                           // unwritten rows may hold anything
+        if (hidden[u]) {                                            // unwritten rows may hold anything
 #pragma unroll
           for (int i = 0; i < 8; ++i) vf[i] = 0.f;
         }
@@ -369,7 +392,7 @@ attention_decode_bulk_kernel(const __nv_bfloat16* __restrict__ q, int q_row_stri
   }
   if (max_splits > 1 && counters)
     merge_splits_if_last<D>(counters + (size_t)seq * gridDim.y + blockIdx.y, part_acc, part_ml,
-                            (size_t)seq * nq + (size_t)kvh0 * R, hg_here * R, min(pos / split_keys + 1, max_splits), max_splits,
+                            (size_t)seq * nq + (size_t)kvh0 * R, hg_here * R, min(pos / split_keys - first_split + 1, max_splits), max_splits,
                             out + (size_t)t * out_row_stride + (size_t)kvh0 * R * D);
 }
 
@@ -380,13 +403,14 @@ __global__ void __launch_bounds__(64)
 attention_decode_bulk_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                      const int* __restrict__ token_of_seq, const int* __restrict__ positions,
                                      __nv_bfloat16* __restrict__ out, int out_row_stride, int max_splits,
-                                     int nq, int head_dim, int split_keys) {
+                                     int nq, int head_dim, int split_keys, int window) {
   chain_wait();
   __shared__ float s_w[kCombineMaxSplits];
   __shared__ float s_red[2];
   const int h = blockIdx.x, seq = blockIdx.y, tid = threadIdx.x;
   const int t = token_of_seq[seq];
-  const int n_splits = min(positions[t] / split_keys + 1, max_splits);   // never beyond what the split kernel wrote
+  const int k_lo = window > 0 ? max(positions[t] - window + 1, 0) : 0;
+  const int n_splits = min(positions[t] / split_keys - k_lo / split_keys + 1, max_splits);   // never beyond what the split kernel wrote
   const size_t base = ((size_t)seq * nq + h) * max_splits;
   float m_i = -INFINITY, l_i = 0.f;
   if (tid < n_splits) { m_i = part_ml[(base + tid) * 2]; l_i = part_ml[(base + tid) * 2 + 1]; }
@@ -439,13 +463,14 @@ int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, con
                        const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                        float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
                        int split_keys, float scale_log2, void* out, int out_row_stride, int* status, int* counters, int head_group,
-                       cudaStream_t s) {
+                       int window, int keep_first, cudaStream_t s) {
   const int hg = decode_head_group(nkv, D, page_size, split_keys, head_group);
   if (hg <= 0) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: %d heads per block with pages of %d and splits of %d", head_group, page_size, split_keys);
   constexpr int STAGE_BYTES = kDecWarps * (32 / (D / 8)) * kKeysPerGroup * D * 2;
   const size_t smem = 2 * kStages * STAGE_BYTES + 64 + (size_t)kDecWarps * R * (D + 2) * sizeof(float) + 128 +
-                      (size_t)(split_keys / page_size + 2) * sizeof(int);
-  if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: split of %d keys in pages of %d", split_keys, page_size);
+                      (size_t)(split_keys / page_size + 2 + (window > 0 ? keep_first / page_size + 1 : 0)) * sizeof(int);
+  if (smem > 200 * 1024)
+    return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: split of %d keys and %d kept keys in pages of %d", split_keys, keep_first, page_size);
   auto kern = attention_decode_bulk_kernel<D, R>;
   static size_t configured = 0;
   if (smem > configured) {
@@ -455,7 +480,8 @@ int launch_decode_bulk(const void* q, int q_row_stride, const void* k_pages, con
   }
   launch_chained(kern, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kDecThreads), smem, s, (const __nv_bfloat16*)q, q_row_stride,
       (const __nv_bfloat16*)k_pages, (const __nv_bfloat16*)v_pages, block_tables, max_pages, token_of_seq, positions,
-      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride, status, counters);
+      part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride, status, counters,
+      window, keep_first);
   return check_launch("attention_decode_bulk");
 }
 
@@ -464,12 +490,12 @@ int dispatch_group(int r, const void* q, int q_row_stride, const void* k_pages, 
                    const int* block_tables, int max_pages, const int* token_of_seq, const int* positions,
                    float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int page_size,
                    int split_keys, float scale_log2, void* out, int out_row_stride, int* status, int* counters, int head_group,
-                   cudaStream_t s) {
+                   int window, int keep_first, cudaStream_t s) {
 #define ERB_R(RR)                                                                                              \
   case RR: return launch_decode_bulk<D, RR>(q, q_row_stride, k_pages, v_pages, block_tables, max_pages,        \
                                             token_of_seq, positions, part_acc, part_ml, max_splits, n_seqs, nq, \
                                             nkv, page_size, split_keys, scale_log2, out, out_row_stride,       \
-                                            status, counters, head_group, s);
+                                            status, counters, head_group, window, keep_first, s);
   switch (r) { ERB_R(1) ERB_R(2) ERB_R(3) ERB_R(4) ERB_R(5) ERB_R(6) ERB_R(7) ERB_R(8) }
 #undef ERB_R
   return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: %d query heads per kv head (at most %d)", r, kMaxGroup);
@@ -821,7 +847,7 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
   // a single split wrote the result itself; with counters the block that finishes last merges the splits
   if ((rc = check_launch("attention_decode_gqa")) || max_splits == 1 || counters) return rc;
   launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
-      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
+      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys, 0);
   return check_launch("attention_decode_bulk_combine");
 }
 
@@ -840,16 +866,19 @@ ERB_EXPORT int erb_attention_decode_bulk_head_group(int nkv, int head_dim, int p
 }
 
 // Same contract as the general decode entry point (scratch provided by the caller, splits at
-// absolute multiples of split_keys), for bfloat16 with head_dim 32 / 64 / 128, no window, at most
-// 8 query heads per kv head, and page rows that are 16-byte multiples.
+// absolute multiples of split_keys, counted from the one that holds the window's first key), for bfloat16
+// with head_dim 32 / 64 / 128, at most 8 query heads per kv head, and page rows that are 16-byte multiples.
+// window > 0: the token sees its last `window` keys (its own included) and the first `keep_first` ones.
 ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const void* k_pages, const void* v_pages,
                                          const int* block_tables, int max_pages, const int* token_of_seq,
                                          const int* positions, void* out, int out_row_stride, float* part_acc,
                                          float* part_ml, int max_splits, int n_seqs, int nq, int nkv, int head_dim,
                                          int page_size, int split_keys, float scale, int* status, int* counters,
-                                         int head_group, void* stream) {
+                                         int head_group, int window, int keep_first, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
   if (nq <= 0 || nkv <= 0 || nq % nkv) return fail(ERB_ERR_ARG, "attention_decode_bulk: bad head counts");
+  window = window > 0 ? window : 0;
+  keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   if (max_splits <= 0 || split_keys <= 0 || !part_acc || !part_ml || !status || page_size <= 0)
     return fail(ERB_ERR_ARG, "attention_decode_bulk: bad arguments");
   if (q_row_stride % 8 || ((uintptr_t)q & 15) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
@@ -864,18 +893,18 @@ ERB_EXPORT int erb_attention_decode_bulk(const void* q, int q_row_stride, const 
   switch (head_dim) {
     case 32: rc = dispatch_group<32>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                      positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
-                                     scale_log2, out, out_row_stride, status, counters, head_group, s); break;
+                                     scale_log2, out, out_row_stride, status, counters, head_group, window, keep_first, s); break;
     case 64: rc = dispatch_group<64>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                      positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size, split_keys,
-                                     scale_log2, out, out_row_stride, status, counters, head_group, s); break;
+                                     scale_log2, out, out_row_stride, status, counters, head_group, window, keep_first, s); break;
     case 128: rc = dispatch_group<128>(r, q, q_row_stride, k_pages, v_pages, block_tables, max_pages, token_of_seq,
                                        positions, part_acc, part_ml, max_splits, n_seqs, nq, nkv, page_size,
-                                       split_keys, scale_log2, out, out_row_stride, status, counters, head_group, s); break;
+                                       split_keys, scale_log2, out, out_row_stride, status, counters, head_group, window, keep_first, s); break;
     default: return fail(ERB_ERR_UNSUPPORTED, "attention_decode_bulk: head_dim %d (takes 32, 64, 128)", head_dim);
   }
   // a single split wrote the result itself; with counters the block that finishes last merges the splits
   if (rc || max_splits == 1 || counters) return rc;
   launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
-      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys);
+      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys, window);
   return check_launch("attention_decode_bulk_combine");
 }

@@ -59,10 +59,10 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_float, c_void_p],
     "erb_attention_prefill_tc": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
-                                 c_int, c_int, c_int, c_void_p, c_void_p, c_void_p],
+                                 c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "erb_attention_decode_bulk": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
                                   c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_float, c_void_p, c_void_p, c_int, c_void_p],
+                                  c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "erb_attention_decode_gqa": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_float, c_void_p, c_void_p, c_void_p],
@@ -1095,8 +1095,9 @@ def attention_decode(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tens
 
 def decode_bulk_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,
                           max_splits: int = 1) -> bool:
-    """Shapes the bulk-copy decode kernel takes; everything else goes to the general decode kernel."""
-    return (dtype == torch.bfloat16 and head_dim in (32, 64, 128) and window <= 0
+    """Shapes the bulk-copy decode kernel takes (with or without a window); everything else goes to the general
+    decode kernel."""
+    return (dtype == torch.bfloat16 and head_dim in (32, 64, 128)
             and n_q_heads // n_kv_heads <= 8 and max_splits <= 64)
 
 
@@ -1126,8 +1127,11 @@ def reset_split_counters() -> None:
 def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                           token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                           scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
-                          status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS, head_group: int = 0) -> None:
+                          status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS, head_group: int = 0, window: int = 0,
+                          keep_first: int = 0) -> None:
     """``attention_decode`` for bfloat16 with keys and values streamed by bulk asynchronous copies.
+    ``window`` > 0: the last ``window`` keys and the first ``keep_first``; the splits are counted from the one
+    that holds the window's first key, and the first of them also walks the kept keys.
     The splits of a sequence are merged by the block that finishes last (``split_counters``), so
     this is one launch.  ``head_group``: kv heads per block (a power of two; 0: as many as make a
     page's copy about 8 KB)."""
@@ -1147,7 +1151,7 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
           v_pages.data_ptr(), block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
           n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(),
-          split_counters(q.device, n_seqs * nkv).data_ptr(), int(head_group), _stream())
+          split_counters(q.device, n_seqs * nkv).data_ptr(), int(head_group), int(window), int(keep_first), _stream())
 
 
 @functools.lru_cache(maxsize=4096)
@@ -1191,9 +1195,9 @@ PREFILL_TC_ROWS = 256
 
 
 def prefill_tc_supported(dtype: torch.dtype, head_dim: int, window: int, page_size: int = 16) -> bool:
-    """Shapes the tensor-core prefill kernel takes (bfloat16, head size 64, no window, pages of 8 to
-    128 tokens, a power of two); everything else goes to the general row kernel."""
-    return (dtype == torch.bfloat16 and head_dim == 64 and window <= 0
+    """Shapes the tensor-core prefill kernel takes (bfloat16, head size 64, with or without a window, pages
+    of 8 to 128 tokens, a power of two); everything else goes to the general row kernel."""
+    return (dtype == torch.bfloat16 and head_dim == 64
             and 8 <= page_size <= 128 and page_size & (page_size - 1) == 0)
 
 
@@ -1223,8 +1227,10 @@ def prefill_tc_scratch_floats(n_rows: int, n_q_heads: int, key_splits: int) -> t
 def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                          seq_starts: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_blocks: int,
                          n_q_heads: int, scale: float, status: torch.Tensor, key_splits: int = 1, first_row: int = 0,
-                         part_o: torch.Tensor | None = None, part_ml: torch.Tensor | None = None) -> None:
-    """Causal attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64, no window).
+                         part_o: torch.Tensor | None = None, part_ml: torch.Tensor | None = None, window: int = 0,
+                         keep_first: int = 0) -> None:
+    """Causal attention of prompt portions on tcgen05 tensor cores (bfloat16, head_dim 64).  ``window`` > 0: a
+    query sees the last ``window`` keys (its own included) and the first ``keep_first`` of its sequence.
 
     ``qkv`` / ``out``: row t is token t of the batch (the q heads lead each qkv row);
     ``seq_starts`` int32 ``[n + 1]``: token offsets of the n sequences to process, whose block tables
@@ -1251,7 +1257,7 @@ def attention_prefill_tc(qkv: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
           v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], seq_starts.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), n_seqs, int(n_blocks), n_q_heads, nkv, d, page_size,
           float(scale), status.data_ptr(), int(key_splits), int(first_row), qkv.shape[0] - int(first_row), _ptr(part_o), _ptr(part_ml),
-          _stream())
+          int(window), int(keep_first), _stream())
     if key_splits > 1:
         launch_counts["own"] += 1          # the merge of the ranges
 

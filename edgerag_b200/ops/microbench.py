@@ -86,7 +86,9 @@ def _paged(batch: int, context: int, nkv: int, d: int, page: int, dtype, shuffle
 
 def decode_attention(a) -> dict:
     dtype = torch.bfloat16 if a.dtype == "bfloat16" else torch.float32
-    nbytes = 2 * a.batch * a.context * a.kv_heads * a.head_dim * (2 if dtype == torch.bfloat16 else 4)
+    window, keep = getattr(a, "window", 0), getattr(a, "keep_first", 0)
+    seen = min(a.context, window + keep) if window > 0 else a.context       # keys a query reads
+    nbytes = 2 * a.batch * seen * a.kv_heads * a.head_dim * (2 if dtype == torch.bfloat16 else 4)
     # --cold: rotate over so many caches that each launch finds its keys and values in DRAM, as a
     # step does whose weights have passed through L2 since the layer's cache was last read
     reps = max(2, int(300e6 // nbytes) + 1) if a.cold else 1
@@ -103,10 +105,15 @@ def decode_attention(a) -> dict:
     tok = torch.arange(a.batch, dtype=torch.int32, device="cuda")
     if a.split <= 0:        # as the engine chooses it: from the batch and a power-of-two bound on the context
         bound, granule = kernels.context_bound(-(-a.context // a.page))
+        if window > 0:
+            bound = min(bound, -(-(window + keep) // a.page))
+            granule = bound
         a.split, heads = kernels.choose_decode_plan(a.batch, a.kv_heads, bound * a.page, a.page, a.head_dim, a.kernel != "bulk",
                                                     granule * a.page)
         a.head_group = a.head_group or heads
     splits = (a.context - 1) // a.split + 1
+    if window > 0 and a.kernel != "gqa":
+        splits = min(splits, window // a.split + 2)
     acc_n, ml_n = kernels.decode_scratch_floats(a.batch, a.heads, a.head_dim, splits)
     acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -116,14 +123,14 @@ def decode_attention(a) -> dict:
                                                   status, split_keys=a.split)
     elif a.kernel == "bulk":
         fn = lambda: kernels.attention_decode_bulk(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
-                                                   status, split_keys=a.split, head_group=a.head_group)
+                                                   status, split_keys=a.split, head_group=a.head_group, window=window, keep_first=keep)
     else:
         fn = lambda: kernels.attention_decode(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
-                                              split_keys=a.split)
+                                              split_keys=a.split, window=window, keep_first=keep)
     us = _time(fn, max(a.iters, 2 * reps), a.warmup)
     return {"case": "decode-attention", "kernel": a.kernel, "split": a.split, "head_group": a.head_group, "us": round(us, 2),
             "bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "frac_hbm": round(nbytes / us / 1e3 / HBM_GBS, 4),
-            "status": int(status), "from_dram": bool(a.cold) or nbytes > 126e6}
+            "status": int(status), "from_dram": bool(a.cold) or nbytes > 126e6, "window": window, "keep_first": keep}
 
 
 def prefill_attention(a) -> dict:
@@ -138,20 +145,28 @@ def prefill_attention(a) -> dict:
     seq_of = torch.zeros(a.tokens, dtype=torch.int32, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     scale = a.head_dim ** -0.5
+    window, keep = getattr(a, "window", 0), getattr(a, "keep_first", 0)
     if a.kernel == "tc":
         blocks = kernels.prefill_tc_blocks([a.tokens])
-        ranges = a.key_splits or kernels.prefill_tc_key_splits(blocks, a.heads, total, qkv.device)
+        reach = min(total, window + keep + kernels.PREFILL_TC_ROWS) if window > 0 else total
+        ranges = a.key_splits or kernels.prefill_tc_key_splits(blocks, a.heads, reach, qkv.device)
         need_o, need_ml = kernels.prefill_tc_scratch_floats(a.tokens, a.heads, ranges)
         part_o, part_ml = torch.empty(need_o, device="cuda"), torch.empty(need_ml, device="cuda")
         fn = lambda: kernels.attention_prefill_tc(qkv, kp, vp, tables, starts, pos, out, blocks, a.heads, scale, status,  # noqa: E731
-                                                  key_splits=ranges, part_o=part_o, part_ml=part_ml)
+                                                  key_splits=ranges, part_o=part_o, part_ml=part_ml, window=window, keep_first=keep)
     else:
-        fn = lambda: kernels.attention_rows(qkv, kp, vp, tables, seq_of, pos, out, a.heads, scale)  # noqa: E731
+        fn = lambda: kernels.attention_rows(qkv, kp, vp, tables, seq_of, pos, out, a.heads, scale, window=window,  # noqa: E731
+                                            keep_first=keep)
     us = _time(fn, a.iters, a.warmup)
-    pairs = a.tokens * a.past + a.tokens * (a.tokens + 1) / 2
+    if window > 0:      # (query, key) pairs that are seen: the window's keys and the kept ones before it
+        p = torch.arange(a.past, total, dtype=torch.float64)
+        lo = (p - window + 1).clamp_min(0)
+        pairs = float((p - lo + 1 + torch.minimum(lo, torch.tensor(float(keep)))).sum())
+    else:
+        pairs = a.tokens * a.past + a.tokens * (a.tokens + 1) / 2
     flops = 4.0 * a.heads * a.head_dim * pairs
     return {"case": "prefill-attention", "kernel": a.kernel, "us": round(us, 2), "tflops": round(flops / us / 1e6, 1),
-            "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4), "status": int(status)}
+            "frac_bf16": round(flops / us / 1e6 / BF16_TFLOPS, 4), "status": int(status), "window": window, "keep_first": keep}
 
 
 def linear(a) -> dict:
@@ -392,6 +407,8 @@ def main(argv=None) -> int:
     att.add_argument("--kv-heads", type=int, default=32)
     att.add_argument("--head-dim", type=int, default=64)
     att.add_argument("--page", type=int, default=16)
+    att.add_argument("--window", type=int, default=0, help="keys a query sees behind itself (0: all)")
+    att.add_argument("--keep-first", type=int, default=0, help="with a window: first keys that stay visible")
     att.add_argument("--sequential-pages", action="store_true", help="pages in order instead of shuffled")
     d = sub.add_parser("decode-attention", parents=[common, att])
     d.add_argument("--batch", type=int, default=8)

@@ -15,8 +15,8 @@ encoding (``values_are_keys``: no value projection; the cache still holds keys a
 names (``names``).  With any of bias, norm or shared values the step after the product is one kernel
 (``kernels.qk_prepare``) that also writes the cache.
 
-Single new tokens go through the split-KV decode kernel, portions of prompts through the row
-kernel; both read keys and values straight from the pages (no gather copy, unlike
+Single new tokens go through the split-KV decode kernels, portions of prompts through the tensor-core
+kernel (bfloat16, heads of 64, with or without a window) or the row kernel; all read keys and values straight from the pages (no gather copy, unlike
 edgerag/cache/paged.py:208-238).
 """
 
@@ -124,10 +124,13 @@ class Attention(Mixer):
                                                                               ctx.page_size, kernels.DECODE_SPLIT_KEYS)
             if ctx.batch_invariant:     # one plan for every batch: a sequence's sums are then added in one order
                 split, heads_per_block = kernels.DECODE_SPLIT_KEYS, 0
+            elif self.window > 0:       # a token reads its window and the kept keys, however long its context is
+                reach = min(ctx.max_keys_bound(), -(-(self.window + self.keep_first) // ctx.page_size) * ctx.page_size)
+                split, heads_per_block = kernels.choose_decode_plan(nd, self.n_kv, reach, ctx.page_size, d,
+                                                                    self.dtype != torch.bfloat16, reach)
             else:
                 split, heads_per_block = kernels.choose_decode_plan(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size, d,
-                                                                    grouped or self.window > 0 or self.dtype != torch.bfloat16,
-                                                                    ctx.keys_granule())
+                                                                    grouped or self.dtype != torch.bfloat16, ctx.keys_granule())
             max_splits = ctx.decode_splits(self.window, split)
             need_acc, need_ml = kernels.decode_scratch_floats(nd, self.n_q, d, max_splits)
             part_acc = ctx.buf("attn.part_acc", (need_acc,), torch.float32)
@@ -139,7 +142,8 @@ class Attention(Mixer):
             elif kernels.decode_bulk_supported(self.dtype, d, self.window, self.n_q, self.n_kv, max_splits):
                 kernels.attention_decode_bulk(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                               out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
-                                              split_keys=split, head_group=heads_per_block)
+                                              split_keys=split, head_group=heads_per_block, window=self.window,
+                                              keep_first=self.keep_first)
             else:
                 kernels.attention_decode(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                          out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits,
@@ -147,7 +151,10 @@ class Attention(Mixer):
         if n > nd and kernels.prefill_tc_supported(self.dtype, d, self.window, ctx.page_size):
             blocks = kernels.prefill_tc_blocks(ctx.host_q_len[nd:])
             # a portion that is short against its past: its few blocks' keys are cut into ranges
-            ranges = kernels.prefill_tc_key_splits(blocks, self.n_q, ctx.max_keys_bound(), qkv.device)
+            reach = ctx.max_keys_bound()
+            if self.window > 0:         # what a block of rows can see: its rows' windows and the kept first keys
+                reach = min(reach, self.window + kernels.PREFILL_TC_ROWS + self.keep_first)
+            ranges = kernels.prefill_tc_key_splits(blocks, self.n_q, reach, qkv.device)
             part_o = part_ml = None
             if ranges > 1:
                 need_o, need_ml = kernels.prefill_tc_scratch_floats(n, self.n_q, ranges)
@@ -155,7 +162,7 @@ class Attention(Mixer):
                 part_ml = ctx.buf("attn.range_ml", (need_ml,), torch.float32)
             kernels.attention_prefill_tc(qkv, k_pages, v_pages, tables[nd:], ctx.seq_starts[nd:], ctx.positions, out, blocks,
                                          self.n_q, self.scale, ctx.status, key_splits=ranges, first_row=nd, part_o=part_o,
-                                         part_ml=part_ml)
+                                         part_ml=part_ml, window=self.window, keep_first=self.keep_first)
         elif n > nd:
             kernels.attention_rows(qkv[nd:], k_pages, v_pages, tables, ctx.seq_of_token[nd:], ctx.positions[nd:],
                                    out[nd:], self.n_q, self.scale, window=self.window, keep_first=self.keep_first)
