@@ -494,7 +494,7 @@ def run_reference(args) -> dict:
     }
 
 
-# --- the Dokodra design beside the Llama decoder at equal sizes ------------------------------------
+# --- the Dokodra and Vokusun designs beside the Llama decoder at equal sizes ------------------------------------
 
 DESIGN_SIZES = {
     "w1024": {"width": 1024, "ff": 4096, "vocab": 32768,
@@ -528,17 +528,38 @@ def dokodra_config(size: dict, n_layers: int) -> dict:
             "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "layers": layers}
 
 
-def llama_config(size: dict, n_layers: int) -> dict:
+def llama_config(size: dict, n_layers: int, kv_heads: int | None = None) -> dict:
     heads = size["width"] // 64
     return dict(CONFIG_2B, num_hidden_layers=n_layers, hidden_size=size["width"], num_attention_heads=heads,
-                num_key_value_heads=heads, intermediate_size=size["ff"], vocab_size=size["vocab"], rope_theta=10000.0,
+                num_key_value_heads=kv_heads or heads, intermediate_size=size["ff"], vocab_size=size["vocab"], rope_theta=10000.0,
                 tie_word_embeddings=False)
 
 
+#: the Vokusun sizes beside DESIGN_SIZES: windowed attention with heads of 64 (a quarter as many key/value heads)
+#: and the latent attention of the sizes above
+VOKUSUN_WINDOW = {"size": 1024, "keep_first": 16}
+
+
+def vokusun_config(size: dict, n_runs: int) -> dict:
+    """``n_runs`` layer runs: windowed attention, latent attention, windowed attention, repeated; from five runs
+    on the second and third layer are walked twice with the same weights (so two layers fewer are stored)."""
+    heads = size["width"] // 64
+    window = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 64, "vdim": 64, "scale": 64 ** -0.5,
+              "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 2.0}}, "mask": dict(VOKUSUN_WINDOW)}
+    att = {k: v for k, v in size["att"].items() if k != "q_rank"}
+    latent = dict(att, scale=(att["dim"] + att["rot_dim"]) ** -0.5, rot={"base": 1000000.0, "dims": att["rot_dim"]})
+    mlp = {"kind": "dense", "ff": size["ff"]}
+    looped = n_runs >= 5
+    layers = [{"type": "latent_attention", "mixer": dict(latent), "mlp": mlp} if i % 3 == 1 else
+              {"type": "attention", "mixer": dict(window), "mlp": mlp} for i in range(n_runs - 2 if looped else n_runs)]
+    return {"architecture": "Vokusun", "width": size["width"], "vocab": size["vocab"], "norm": {"eps": 1e-5}, "layers": layers,
+            "loop": {"start": 1, "stop": 3, "times": 2} if looped else None}
+
+
 def run_designs(args) -> dict:
-    """Prefill (one portion of 2,048 tokens) and decode (batch 1 and --batch at a context of 2,048) of Dokodra
-    and of the Llama decoder at the same width, feed-forward size, vocabulary and layer count, random
-    weights, plus the new design's kernels alone against their rooflines."""
+    """Prefill (one portion of 2,048 tokens) and decode (batch 1 and --batch at a context of 2,048) of one design
+    (--design) and of the Llama decoder at the same width, feed-forward size, vocabulary and number of layer
+    runs, random weights, plus the design's kernels alone against their rooflines."""
     import types
 
     import torch
@@ -608,6 +629,8 @@ def run_designs(args) -> dict:
         torch.cuda.empty_cache()
         return res
 
+    if args.design == "vokusun":
+        return run_vokusun(args, measure, n_layers, block, clocks, peak_source, microbench)
     for name, size in DESIGN_SIZES.items():
         out[name] = {"layers": n_layers, "dokodra": measure(dokodra_config(size, n_layers), size["vocab"]),
                      "llama": measure(llama_config(size, n_layers), size["vocab"])}
@@ -635,6 +658,47 @@ def run_designs(args) -> dict:
             "sizes": out, "kernels": kern, "clocks": clocks.record()}
 
 
+def run_vokusun(args, measure, n_runs: int, block: int, clocks, peak_source: str, microbench) -> dict:
+    """Vokusun beside the Llama decoder with the same grouping of key/value heads, then its attention kernels beside
+    the Llama decoder's at equal work, then which kernels a step of each spends its time in."""
+    import types
+
+    out: dict = {}
+    for name, size in DESIGN_SIZES.items():
+        kv = max(1, size["width"] // 64 // 4)
+        out[name] = {"layer_runs": n_runs, "vokusun": measure(vokusun_config(size, n_runs), size["vocab"]),
+                     "llama": measure(llama_config(size, n_runs, kv), size["vocab"])}
+    size = DESIGN_SIZES["w2048"]
+    att, win, keep = size["att"], VOKUSUN_WINDOW["size"], VOKUSUN_WINDOW["keep_first"]
+    ns = lambda **kw: types.SimpleNamespace(dtype="bfloat16", iters=10, warmup=3, page=block, sequential_pages=False, **kw)  # noqa: E731
+    heads = dict(heads=32, kv_heads=8, head_dim=64)
+    lat = dict(heads=att["heads"], rank=att["kv_rank"], rot=att["rot_dim"], split=0, kernel="mma")
+    pre = lambda tokens, **kw: microbench.prefill_attention(ns(tokens=tokens, past=0, kernel="tc", key_splits=0, **heads, **kw))  # noqa: E731
+    dec = lambda **kw: microbench.decode_attention(ns(batch=64, split=0, head_group=0, cold=True, **heads, **kw))  # noqa: E731
+    kern = {
+        "window_attention_prefill_2048": pre(2048, window=win, keep_first=keep),
+        "llama_attention_prefill_2048": pre(2048),
+        "window_attention_prefill_8192": pre(8192, window=win, keep_first=keep),
+        "llama_attention_prefill_8192": pre(8192),
+        # a token of a windowed layer reads its window and the kept keys: the same bytes as a context of that length
+        "window_attention_decode_b64_ctx8192": dec(context=8192, kernel="bulk", window=win, keep_first=keep),
+        "llama_attention_decode_b64_ctx1024_bulk": dec(context=1024, kernel="bulk"),
+        "llama_attention_decode_b64_ctx1024_gqa": dec(context=1024, kernel="gqa"),
+        "latent_attention_decode_b8_ctx8192": microbench.latent_attention(ns(batch=8, context=8192, tokens=0, past=0, cold=True, **lat)),
+        "latent_attention_prefill_2048": microbench.latent_attention(ns(batch=1, context=0, tokens=2048, past=0, cold=False, **lat)),
+    }
+    steps = {}
+    for name, cfg in (("vokusun", vokusun_config(size, 3)), ("llama", llama_config(size, 3, 8))):
+        steps[name] = microbench.step_kernels(types.SimpleNamespace(config=cfg, vocab=size["vocab"], layers=3, heads=32, kv_heads=8, batch=args.batch, context=2048,
+                                                                    tokens=2048, iters=4, rows=16))
+    return {"metric": "design_compare", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
+            "data": "synthetic", "impl": "ours", "higher_is_better": True,
+            "config": {"designs": ["Vokusun", "Llama decoder"], "prefill_tokens": 2048, "decode_context": 2048,
+                       "decode_batches": sorted({1, args.batch}), "page_tokens": block, "window": VOKUSUN_WINDOW, "peaks": peak_source,
+                       "l2": "decode: weights and cache larger than L2 at w2048; kernels: caches rotated (cold)"},
+            "sizes": out, "kernels": kern, "step_kernels": steps, "clocks": clocks.record()}
+
+
 def _tensors_of(model) -> list:
     import torch
 
@@ -660,8 +724,10 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--workload", choices=["decode", "mixed", "continuous", "designs"], default="decode",
                     help="decode: the headline measurement; mixed / continuous: the serving workloads of the "
-                         "256M and 500M decoders through Engine.generate; designs: prefill and decode of the Dokodra "
-                         "design beside the Llama decoder at equal sizes, and its kernels against their rooflines")
+                         "256M and 500M decoders through Engine.generate; designs: prefill and decode of one design "
+                         "(--design) beside the Llama decoder at equal sizes, and its kernels against their rooflines")
+    ap.add_argument("--design", choices=["dokodra", "vokusun"], default="dokodra",
+                    help="with --workload designs: the design that is measured beside the Llama decoder")
     ap.add_argument("--ref-cpu-check", action="store_true",
                     help="with --impl reference: a dry run of the reference arm's loop at toy sizes on the CPU")
     args = ap.parse_args()

@@ -201,7 +201,8 @@ def linear(a) -> dict:
 
 
 def step_kernels(a) -> dict:
-    """Which kernels a step's time goes to: the SmolVLM-2.2B layer sizes with ``--layers`` layers, a
+    """Which kernels a step's time goes to: the SmolVLM-2.2B layer sizes with ``--layers`` layers (or the
+    model of ``a.config``, a config.json as a dict, with ``a.vocab``), a
     prefill of ``--tokens`` tokens and decode steps of ``--batch`` sequences at ``--context``, run
     eagerly under the CUDA activity tracer without chained launches (so that a kernel's time is its
     own).  The microseconds are per launch and carry the tracer's overhead: read them as shares."""
@@ -217,19 +218,22 @@ def step_kernels(a) -> dict:
            "num_attention_heads": a.heads, "num_key_value_heads": a.kv_heads, "head_dim": 64, "intermediate_size": 8192,
            "vocab_size": 49155, "rope_theta": 273768.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
            "hidden_act": "silu", "max_position_embeddings": 8192, "pad_token_id": 0}
+    cfg = getattr(a, "config", None) or cfg
+    vocab = getattr(a, "vocab", None) or 49155
+    rows_shown = getattr(a, "rows", 12)
     eng = Engine.from_config(cfg, 0, 0.02, EngineOptions(
         dtype="bfloat16", block_size=16, num_blocks=a.batch * (a.context // 16 + 2) + a.tokens // 16 + 64,
         max_batch_size=a.batch + 2, chunk_size=a.tokens, max_step_tokens=a.tokens + a.batch, max_model_len=a.context + 8,
         cuda_graphs=False))
     r = eng.runner
-    ids = torch.randint(0, 49155, (a.tokens,)).tolist()
+    ids = torch.randint(0, vocab, (a.tokens,)).tolist()
 
     def table(prof, launches_of):
         rows = [(e.key, e.device_time_total / max(1, e.count), e.count) for e in prof.key_averages() if e.device_time_total > 0]
         total = sum(us * n for _, us, n in rows)
         rows.sort(key=lambda x: -x[1] * x[2])
         return {"total_us_per_" + launches_of[0]: round(total / launches_of[1], 1),
-                "kernels": [{"name": k[:70], "us": round(us, 2), "calls": n, "share": round(us * n / total, 3)} for k, us, n in rows[:12]]}
+                "kernels": [{"name": k[:70], "us": round(us, 2), "calls": n, "share": round(us * n / total, 3)} for k, us, n in rows[:rows_shown]]}
 
     def prefill(name):
         r.admit(name)
