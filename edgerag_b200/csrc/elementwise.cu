@@ -840,6 +840,134 @@ add_layernorm_kernel(float* __restrict__ hidden, const T* __restrict__ delta, co
     Elem<T>::store(y + i, (row_cache[i] - mean) * rs * w[i] + b[i]);
 }
 
+// The same with 16-byte accesses and the row in registers: a thread owns up to V groups of four neighbouring
+// elements (group g of the row belongs to thread g % blockDim.x), so the row is read once, all of a thread's
+// loads are in flight together, and only the four block sums stand between the load and the store.  The sums
+// are taken in the order of the kernel above's threads only where the block sizes agree; both kernels are
+// within rounding of each other, and a launch always takes the same one for the same width.
+template <typename T, int V>
+__global__ void __launch_bounds__(256)
+add_layernorm_vec4_kernel(float* __restrict__ hidden, const T* __restrict__ delta, const float* __restrict__ parts, int n_parts,
+                          size_t part_stride, const float* __restrict__ post_w, const float* __restrict__ post_b, float post_eps,
+                          const float* __restrict__ w, const float* __restrict__ b, float eps, T* __restrict__ out, int out_ld,
+                          const int* __restrict__ rows, int width, int write_back) {
+  __shared__ float scratch[32];
+  const int groups = width >> 2;
+  const float inv_w = 1.f / (float)width;
+  int col[V];
+  bool on[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    const int g = threadIdx.x + v * blockDim.x;
+    on[v] = g < groups;
+    col[v] = 4 * g;
+  }
+  chain_wait();
+  const int o = blockIdx.x;
+  const int r = rows ? rows[o] : o;
+  float* h = hidden + (size_t)r * width;
+  const bool has_delta = delta || parts;
+  float x[V][4], hv[V][4];
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    if (on[v]) load4(h + col[v], hv[v]);
+  }
+  if (has_delta) {
+    float sum = 0.f;
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) x[v][i] = 0.f;
+      if (!on[v]) continue;
+      if (delta) {
+        Pack4<T>::load(delta + (size_t)r * width + col[v], x[v]);
+      } else {
+        const float* ps = parts + (size_t)r * width + col[v];
+        load4(ps, x[v]);
+        for (int sp = 1; sp < n_parts; ++sp) {
+          float more[4];
+          load4(ps + sp * part_stride, more);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) x[v][i] += more[i];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[v][i] = Elem<T>::round(x[v][i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sum += x[v][i];
+    }
+    if (post_w) {
+      const float mean = block_sum(sum, scratch) * inv_w;
+      float sq = 0.f;
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        if (!on[v]) continue;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float c = x[v][i] - mean; sq += c * c; }
+      }
+      const float rs = rsqrtf(block_sum(sq, scratch) * inv_w + post_eps);
+#pragma unroll
+      for (int v = 0; v < V; ++v) {
+        if (!on[v]) continue;
+        float pw[4], pb[4];
+        load4(post_w + col[v], pw);
+        load4(post_b + col[v], pb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) x[v][i] = (x[v][i] - mean) * rs * pw[i] + pb[i];
+      }
+    }
+  }
+  float sum = 0.f;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    if (!on[v]) continue;
+    if (has_delta) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) hv[v][i] += x[v][i];
+      if (write_back) *reinterpret_cast<float4*>(h + col[v]) = make_float4(hv[v][0], hv[v][1], hv[v][2], hv[v][3]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sum += hv[v][i];
+  }
+  if (!out) return;
+  T* y = out + (size_t)o * out_ld;
+  if (!w) {
+#pragma unroll
+    for (int v = 0; v < V; ++v) {
+      if (on[v]) Pack4<T>::store(y + col[v], hv[v]);
+    }
+    return;
+  }
+  const float mean = block_sum(sum, scratch) * inv_w;
+  float sq = 0.f;
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    if (!on[v]) continue;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float c = hv[v][i] - mean; sq += c * c; }
+  }
+  const float rs = rsqrtf(block_sum(sq, scratch) * inv_w + eps);
+#pragma unroll
+  for (int v = 0; v < V; ++v) {
+    if (!on[v]) continue;
+    float ww[4], wb[4], res[4];
+    load4(w + col[v], ww);
+    load4(b + col[v], wb);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) res[i] = (hv[v][i] - mean) * rs * ww[i] + wb[i];
+    Pack4<T>::store(y + col[v], res);
+  }
+}
+
+template <int V>
+void launch_add_layernorm_vec4(int n_rows, int threads, cudaStream_t stream, float* hidden, const elem_t* delta, const float* parts,
+                               int n_parts, size_t part_stride, const float* post_w, const float* post_b, float post_eps,
+                               const float* w, const float* b, float eps, elem_t* out, int out_ld, const int* rows, int width,
+                               int write_back) {
+  launch_chained(add_layernorm_vec4_kernel<elem_t, V>, dim3(n_rows), dim3(threads), 0, stream, hidden, delta, parts, n_parts,
+                 part_stride, post_w, post_b, post_eps, w, b, eps, out, out_ld, rows, width, write_back);
+}
+
 // delta: rows of the element type, or (n_parts > 0) float partial sums [n_parts][rows of hidden][width].
 ERB_EXPORT int erb_add_layernorm(void* hidden, const void* delta, int n_parts, long long part_stride, const float* post_w,
                                  const float* post_b, float post_eps, const float* w, const float* b, float eps, void* out,
@@ -847,6 +975,22 @@ ERB_EXPORT int erb_add_layernorm(void* hidden, const void* delta, int n_parts, l
   if (n_rows <= 0) return ERB_OK;
   if (width <= 0 || (out && out_ld < width) || (w && !b) || (post_w && !post_b) || (post_w && !delta))
     return fail(ERB_ERR_ARG, "add_layernorm: bad sizes or a weight without its bias");
+  const elem_t* d_rows = n_parts > 0 ? (const elem_t*)nullptr : (const elem_t*)delta;
+  const float* d_parts = n_parts > 0 ? (const float*)delta : (const float*)nullptr;
+  const uintptr_t all = (uintptr_t)hidden | (uintptr_t)delta | (uintptr_t)post_w | (uintptr_t)post_b | (uintptr_t)w | (uintptr_t)b |
+                        (uintptr_t)out;
+  if (width % 4 == 0 && width <= 8192 && (all & 15) == 0 && out_ld % 8 == 0 && part_stride % 4 == 0) {
+    // rows of up to 8,192 elements, everything 16-byte aligned: the row stays in registers
+    const int groups = width / 4;
+    const int threads = groups >= 256 ? 256 : (groups + 31) / 32 * 32;
+    const int per_thread = (groups + threads - 1) / threads;
+#define ERB_LN(V) launch_add_layernorm_vec4<V>(n_rows, threads, (cudaStream_t)stream, (float*)hidden, d_rows, d_parts, n_parts,   \
+                                               (size_t)part_stride, post_w, post_b, post_eps, w, b, eps, (elem_t*)out, out_ld, rows, \
+                                               width, write_back)
+    if (per_thread <= 1) ERB_LN(1); else if (per_thread <= 2) ERB_LN(2); else if (per_thread <= 4) ERB_LN(4); else ERB_LN(8);
+#undef ERB_LN
+    return check_launch("add_layernorm");
+  }
   const size_t smem = (size_t)(width + 32) * sizeof(float);
   if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "add_layernorm: width %d does not fit shared memory", width);
   auto kern = add_layernorm_kernel<elem_t>;
@@ -977,6 +1121,136 @@ qk_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_bias,
     for (int i = rot_dim + lane; i < D; i += 32) Elem<T>::store(dst + i, x[i]);
 }
 
+// The same for pairs of neighbours (or no turn at all) and heads of 64, 128 or 256: a lane owns E = D / 32
+// neighbouring entries of every head, so a pair never leaves its lane, rows move in 4- to 32-byte pieces, and a
+// warp walks `hpw` heads of one token with the token's sines and cosines, which it takes once.
+template <typename T, int E> struct LaneRow;
+template <int E> struct LaneRow<float, E> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    if constexpr (E == 2) { const float2 r = *reinterpret_cast<const float2*>(p); v[0] = r.x; v[1] = r.y; }
+    else {
+#pragma unroll
+      for (int i = 0; i < E; i += 4) load4(p + i, v + i);
+    }
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    if constexpr (E == 2) *reinterpret_cast<float2*>(p) = make_float2(v[0], v[1]);
+    else {
+#pragma unroll
+      for (int i = 0; i < E; i += 4) *reinterpret_cast<float4*>(p + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+    }
+  }
+};
+template <int E> struct LaneRow<__nv_bfloat16, E> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    uint32_t raw[E / 2];
+    if constexpr (E == 2) raw[0] = *reinterpret_cast<const uint32_t*>(p);
+    else if constexpr (E == 4) { const uint2 r = *reinterpret_cast<const uint2*>(p); raw[0] = r.x; raw[1] = r.y; }
+    else { const uint4 r = *reinterpret_cast<const uint4*>(p); raw[0] = r.x; raw[1] = r.y; raw[2] = r.z; raw[3] = r.w; }
+#pragma unroll
+    for (int i = 0; i < E / 2; ++i) { v[2 * i] = __uint_as_float(raw[i] << 16); v[2 * i + 1] = __uint_as_float(raw[i] & 0xffff0000u); }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    uint32_t raw[E / 2];
+#pragma unroll
+    for (int i = 0; i < E / 2; ++i) {
+      const __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+      raw[i] = *reinterpret_cast<const uint32_t*>(&two);
+    }
+    if constexpr (E == 2) *reinterpret_cast<uint32_t*>(p) = raw[0];
+    else if constexpr (E == 4) *reinterpret_cast<uint2*>(p) = make_uint2(raw[0], raw[1]);
+    else *reinterpret_cast<uint4*>(p) = make_uint4(raw[0], raw[1], raw[2], raw[3]);
+  }
+};
+
+template <typename T, int E>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+qk_prepare_lanes_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_bias, const float* __restrict__ k_bias,
+                        const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                        const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim,
+                        const int* __restrict__ slots, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nq, int nkv,
+                        int page_size, int values_are_keys, int hpw) {
+  constexpr int D = 32 * E;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, e0 = lane * E;
+  const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
+  const int chunks = (heads + hpw - 1) / hpw;
+  const long long item = (long long)blockIdx.x * kPrepWarps + warp;
+  // the vectors of the model, read while the kernel before this one drains
+  float wq[E], wk[E];
+#pragma unroll
+  for (int i = 0; i < E; ++i) { wq[i] = q_norm ? q_norm[e0 + i] : 1.f; wk[i] = k_norm ? k_norm[e0 + i] : 1.f; }
+  float freq[E / 2];
+#pragma unroll
+  for (int j = 0; j < E / 2; ++j) freq[j] = e0 + 2 * j < rot_dim ? inv_freq[e0 / 2 + j] : 0.f;
+  chain_wait();
+  if (item >= (long long)n_tokens * chunks) return;
+  const int t = (int)(item / chunks), h0 = (int)(item % chunks) * hpw, h1 = min(heads, h0 + hpw);
+  const float pos = (float)positions[t];
+  float cs[E / 2], sn[E / 2];
+#pragma unroll
+  for (int j = 0; j < E / 2; ++j) {
+    cs[j] = 1.f; sn[j] = 0.f;
+    if (e0 + 2 * j < rot_dim) sincosf(pos * freq[j], &sn[j], &cs[j]);
+  }
+  const int slot = slots ? slots[t] : -1;
+  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
+  T* row = qkv + (size_t)t * ld + e0;
+  for (int head = h0; head < h1; ++head) {
+    T* src = row + (size_t)head * D;
+    float x[E];
+    LaneRow<T, E>::load(src, x);
+    if (head >= nq + nkv) {                      // a value head: copied to the cache as it is
+      if (slot >= 0 && v_pages) LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq - nkv)) * page_size + off) * D + e0, x);
+      continue;
+    }
+    const bool is_q = head < nq;
+    const float* bias = is_q ? q_bias : k_bias;
+    if (bias) {
+      float bb[E];
+      LaneRow<float, E>::load(bias + (size_t)(is_q ? head : head - nq) * D + e0, bb);
+#pragma unroll
+      for (int i = 0; i < E; ++i) x[i] += bb[i];
+    }
+    const bool store_kv = !is_q && slot >= 0 && k_pages;
+    if (!is_q && values_are_keys && store_kv && v_pages)
+      LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0, x);
+    if (is_q ? q_norm != nullptr : k_norm != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < E; ++i) ss += x[i] * x[i];
+      const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+#pragma unroll
+      for (int i = 0; i < E; ++i) x[i] = x[i] * rs * (is_q ? wq[i] : wk[i]);
+    }
+    T* dst = is_q ? src : (store_kv ? k_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0 : nullptr);
+    if (!dst) continue;
+#pragma unroll
+    for (int j = 0; j < E / 2; ++j) {
+      if (e0 + 2 * j < rot_dim) {
+        float lo, hi;
+        rotate_pair(x[2 * j], x[2 * j + 1], cs[j], sn[j], lo, hi);
+        x[2 * j] = lo; x[2 * j + 1] = hi;
+      }
+    }
+    LaneRow<T, E>::store(dst, x);
+  }
+}
+
+template <int E>
+void launch_qk_prepare_lanes(cudaStream_t stream, elem_t* qkv, int ld, const float* q_bias, const float* k_bias, const float* q_norm,
+                             const float* k_norm, float eps, const int* positions, const float* inv_freq, int rot_dim,
+                             const int* slots, elem_t* k_pages, elem_t* v_pages, int n_tokens, int nq, int nkv, int page_size,
+                             int values_are_keys) {
+  const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
+  // heads a warp walks: one while the step is small, up to eight when there are warps enough to fill the GPU many times
+  long long hpw = (long long)n_tokens * heads / 4096;
+  hpw = hpw < 1 ? 1 : (hpw > 8 ? 8 : hpw);
+  const long long items = (long long)n_tokens * ((heads + hpw - 1) / hpw);
+  launch_chained(qk_prepare_lanes_kernel<elem_t, E>, dim3((unsigned)((items + kPrepWarps - 1) / kPrepWarps)), dim3(kPrepWarps * 32), 0,
+                 stream, qkv, ld, q_bias, k_bias, q_norm, k_norm, eps, positions, inv_freq, rot_dim, slots, k_pages, v_pages, n_tokens,
+                 nq, nkv, page_size, values_are_keys, (int)hpw);
+}
+
 ERB_EXPORT int erb_qk_prepare(void* qkv, int ld, const float* q_bias, const float* k_bias, const float* q_norm,
                               const float* k_norm, float eps, const int* positions, const float* inv_freq, int rot_dim,
                               int pairs, const int* slots, void* k_pages, void* v_pages, int n_tokens, int nq, int nkv,
@@ -986,6 +1260,15 @@ ERB_EXPORT int erb_qk_prepare(void* qkv, int ld, const float* q_bias, const floa
       (rot_dim && !inv_freq))
     return fail(ERB_ERR_ARG, "qk_prepare: bad sizes (rot_dim %d of head_dim %d)", rot_dim, head_dim);
   if (ld < (nq + nkv + (values_are_keys ? 0 : nkv)) * head_dim) return fail(ERB_ERR_ARG, "qk_prepare: rows too narrow");
+  const uintptr_t all = (uintptr_t)qkv | (uintptr_t)q_bias | (uintptr_t)k_bias | (uintptr_t)k_pages | (uintptr_t)v_pages;
+  if ((pairs || rot_dim == 0) && (head_dim == 64 || head_dim == 128 || head_dim == 256) && ld % 8 == 0 && (all & 15) == 0) {
+#define ERB_QK(E) launch_qk_prepare_lanes<E>((cudaStream_t)stream, (elem_t*)qkv, ld, q_bias, k_bias, q_norm, k_norm, eps, positions, \
+                                             inv_freq, rot_dim, slots, (elem_t*)k_pages, (elem_t*)v_pages, n_tokens, nq, nkv,        \
+                                             page_size, values_are_keys)
+    if (head_dim == 64) ERB_QK(2); else if (head_dim == 128) ERB_QK(4); else ERB_QK(8);
+#undef ERB_QK
+    return check_launch("qk_prepare");
+  }
   const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
   const long long items = (long long)n_tokens * heads;
   const size_t smem = (size_t)kPrepWarps * head_dim * sizeof(float);

@@ -574,18 +574,24 @@ def test_queries_and_keys_made_ready(dtype):
 
     tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     g = torch.Generator().manual_seed(5)
-    for (H, G, d, rot, page, pairs, shared) in ((4, 2, 32, 12, 16, True, True), (3, 3, 48, 48, 8, True, True), (2, 1, 16, 8, 4, False, False),
-                                                (5, 5, 24, 0, 16, True, True)):
-        n = 37
+    # (heads of 64, 128 and 256 with pairs take the kernel in which a lane owns neighbouring entries; many tokens
+    # make a warp of it walk several heads)
+    for (H, G, d, rot, page, pairs, shared, n) in ((4, 2, 32, 12, 16, True, True, 37), (3, 3, 48, 48, 8, True, True, 37),
+                                                   (2, 1, 16, 8, 4, False, False, 37), (5, 5, 24, 0, 16, True, True, 37),
+                                                   (4, 2, 64, 24, 16, True, True, 37), (3, 1, 128, 128, 8, True, True, 21),
+                                                   (2, 2, 256, 64, 16, True, False, 9), (2, 1, 64, 0, 16, True, True, 5),
+                                                   (9, 3, 64, 64, 16, True, True, 1100), (6, 2, 128, 32, 16, True, False, 900),
+                                                   (4, 4, 64, 32, 16, False, False, 37)):
         width = (H + G * (1 if shared else 2)) * d
         x = (torch.randn(n, width, generator=g) * 1.5).to(tdt)
         qb, kb = torch.randn(H * d, generator=g), torch.randn(G * d, generator=g)
         qn, kn = 1 + 0.3 * torch.randn(d, generator=g), 1 + 0.3 * torch.randn(d, generator=g)
         pos = torch.randint(0, 3000, (n,), generator=g, dtype=torch.int32)
-        slots = torch.randperm(5 * page * 3, generator=g)[:n].to(torch.int32)
+        n_pages = max(15, -(-n // page) + 2)
+        slots = torch.randperm(n_pages * page, generator=g)[:n].to(torch.int32)
         slots[3] = -1
         inv = (100.0 ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / max(rot, 1)) / 3.0).float()
-        kp = torch.zeros(15, G, page, d, dtype=tdt).cuda()
+        kp = torch.zeros(n_pages, G, page, d, dtype=tdt).cuda()
         vp = torch.zeros_like(kp)
         xd = x.clone().cuda()
         k.qk_prepare(xd, pos.cuda(), H, G, d, q_bias=qb.cuda(), k_bias=kb.cuda(), q_norm=qn.cuda(), k_norm=kn.cuda(), eps=1e-5,
@@ -611,14 +617,15 @@ def test_queries_and_keys_made_ready(dtype):
         tol = 3e-4 if dtype == "float32" else 3e-2
         assert (xd[:, : H * d].double().cpu() - ready(q, H, qn).reshape(n, H * d)).abs().max() < tol
         kr = ready(kk, G, kn)
+        kc, vc = kp.double().cpu(), vp.double().cpu()
         for t in range(n):
             s = int(slots[t])
             if s < 0:
                 continue
-            assert (kp[s // page, :, s % page].double().cpu() - kr[t]).abs().max() < tol
-            assert (vp[s // page, :, s % page].double().cpu() - vv[t].reshape(G, d)).abs().max() < tol
+            assert (kc[s // page, :, s % page] - kr[t]).abs().max() < tol
+            assert (vc[s // page, :, s % page] - vv[t].reshape(G, d)).abs().max() < tol
         written = {int(s) for s in slots if s >= 0}
-        untouched = [(p, o) for p in range(15) for o in range(page) if p * page + o not in written]
+        untouched = [(p, o) for p in range(n_pages) for o in range(page) if p * page + o not in written]
         assert all(float(kp[p, :, o].abs().max()) == 0 and float(vp[p, :, o].abs().max()) == 0 for p, o in untouched[:50])
 
 
@@ -629,7 +636,8 @@ def test_residual_add_between_two_layer_norms(dtype):
 
     tdt = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
     g = torch.Generator().manual_seed(9)
-    for width in (48, 80, 256, 1000, 4096):
+    # (rows of up to 8,192 entries, a multiple of four, stay in registers; the others are parked in shared memory)
+    for width in (6, 48, 50, 80, 256, 1000, 2048, 4096, 8192, 8200):
         n = 21
         hidden = torch.randn(n, width, generator=g) * 3 + 0.7
         delta = (torch.randn(n, width, generator=g) * 2 - 0.3).to(tdt)
