@@ -1195,44 +1195,54 @@ qk_prepare_lanes_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q
   const int slot = slots ? slots[t] : -1;
   const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
   T* row = qkv + (size_t)t * ld + e0;
-  for (int head = h0; head < h1; ++head) {
-    T* src = row + (size_t)head * D;
-    float x[E];
-    LaneRow<T, E>::load(src, x);
-    if (head >= nq + nkv) {                      // a value head: copied to the cache as it is
-      if (slot >= 0 && v_pages) LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq - nkv)) * page_size + off) * D + e0, x);
-      continue;
+  constexpr int U = 4;                            // heads whose rows are in flight together
+  for (int hb = h0; hb < h1; hb += U) {
+    float xs[U][E];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (hb + u < h1) LaneRow<T, E>::load(row + (size_t)(hb + u) * D, xs[u]);
     }
-    const bool is_q = head < nq;
-    const float* bias = is_q ? q_bias : k_bias;
-    if (bias) {
-      float bb[E];
-      LaneRow<float, E>::load(bias + (size_t)(is_q ? head : head - nq) * D + e0, bb);
 #pragma unroll
-      for (int i = 0; i < E; ++i) x[i] += bb[i];
-    }
-    const bool store_kv = !is_q && slot >= 0 && k_pages;
-    if (!is_q && values_are_keys && store_kv && v_pages)
-      LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0, x);
-    if (is_q ? q_norm != nullptr : k_norm != nullptr) {
-      float ss = 0.f;
-#pragma unroll
-      for (int i = 0; i < E; ++i) ss += x[i] * x[i];
-      const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
-#pragma unroll
-      for (int i = 0; i < E; ++i) x[i] = x[i] * rs * (is_q ? wq[i] : wk[i]);
-    }
-    T* dst = is_q ? src : (store_kv ? k_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0 : nullptr);
-    if (!dst) continue;
-#pragma unroll
-    for (int j = 0; j < E / 2; ++j) {
-      if (e0 + 2 * j < rot_dim) {
-        float lo, hi;
-        rotate_pair(x[2 * j], x[2 * j + 1], cs[j], sn[j], lo, hi);
-        x[2 * j] = lo; x[2 * j + 1] = hi;
+    for (int u = 0; u < U; ++u) {
+      const int head = hb + u;
+      if (head >= h1) break;
+      float* x = xs[u];
+      T* src = row + (size_t)head * D;
+      if (head >= nq + nkv) {                    // a value head: copied to the cache as it is
+        if (slot >= 0 && v_pages) LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq - nkv)) * page_size + off) * D + e0, x);
+        continue;
       }
+      const bool is_q = head < nq;
+      const float* bias = is_q ? q_bias : k_bias;
+      if (bias) {
+        float bb[E];
+        LaneRow<float, E>::load(bias + (size_t)(is_q ? head : head - nq) * D + e0, bb);
+#pragma unroll
+        for (int i = 0; i < E; ++i) x[i] += bb[i];
+      }
+      const bool store_kv = !is_q && slot >= 0 && k_pages;
+      if (!is_q && values_are_keys && store_kv && v_pages)
+        LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0, x);
+      if (is_q ? q_norm != nullptr : k_norm != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < E; ++i) ss += x[i] * x[i];
+        const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
+#pragma unroll
+        for (int i = 0; i < E; ++i) x[i] = x[i] * rs * (is_q ? wq[i] : wk[i]);
+      }
+      T* dst = is_q ? src : (store_kv ? k_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0 : nullptr);
+      if (!dst) continue;
+#pragma unroll
+      for (int j = 0; j < E / 2; ++j) {
+        if (e0 + 2 * j < rot_dim) {
+          float lo, hi;
+          rotate_pair(x[2 * j], x[2 * j + 1], cs[j], sn[j], lo, hi);
+          x[2 * j] = lo; x[2 * j + 1] = hi;
+        }
+      }
+      LaneRow<T, E>::store(dst, x);
     }
-    LaneRow<T, E>::store(dst, x);
   }
 }
 
