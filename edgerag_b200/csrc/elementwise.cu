@@ -1121,9 +1121,10 @@ qk_prepare_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_bias,
     for (int i = rot_dim + lane; i < D; i += 32) Elem<T>::store(dst + i, x[i]);
 }
 
-// The same for pairs of neighbours (or no turn at all) and heads of 64, 128 or 256: a lane owns E = D / 32
-// neighbouring entries of every head, so a pair never leaves its lane, rows move in 4- to 32-byte pieces, and a
-// warp walks `hpw` heads of one token with the token's sines and cosines, which it takes once.
+// The same for pairs of neighbours (or no turn at all) and heads of 64, 128 or 256: a lane owns 8 neighbouring
+// entries of a head, so a pair never leaves its lane, rows move in 16- or 32-byte pieces, 4, 2 or 1 heads of a
+// token are worked on by a warp at a time, and the warp walks `hpw` heads with the token's sines and cosines,
+// which it takes once.
 template <typename T, int E> struct LaneRow;
 template <int E> struct LaneRow<float, E> {
   static __device__ __forceinline__ void load(const float* p, float* v) {
@@ -1163,102 +1164,133 @@ template <int E> struct LaneRow<__nv_bfloat16, E> {
   }
 };
 
-template <typename T, int E>
+template <typename T, int LPH>   // lanes per head: a lane owns 8 neighbouring entries, so the head size is 8 LPH
 __global__ void __launch_bounds__(kPrepWarps * 32)
 qk_prepare_lanes_kernel(T* __restrict__ qkv, int ld, const float* __restrict__ q_bias, const float* __restrict__ k_bias,
                         const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                         const int* __restrict__ positions, const float* __restrict__ inv_freq, int rot_dim,
                         const int* __restrict__ slots, T* __restrict__ k_pages, T* __restrict__ v_pages, int n_tokens, int nq, int nkv,
                         int page_size, int values_are_keys, int hpw) {
-  constexpr int D = 32 * E;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, e0 = lane * E;
+  constexpr int E = 8, D = E * LPH, HW = 32 / LPH;       // HW heads of a token are worked on at a time
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, e0 = (lane % LPH) * E, sub = lane / LPH;
   const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
   const int chunks = (heads + hpw - 1) / hpw;
-  const long long item = (long long)blockIdx.x * kPrepWarps + warp;
+  const int item = blockIdx.x * kPrepWarps + warp;
   // the vectors of the model, read while the kernel before this one drains
   float wq[E], wk[E];
 #pragma unroll
   for (int i = 0; i < E; ++i) { wq[i] = q_norm ? q_norm[e0 + i] : 1.f; wk[i] = k_norm ? k_norm[e0 + i] : 1.f; }
-  float freq[E / 2];
+  // A head has 4 LPH pairs.  With 8 or 16 lanes per head the warp takes every angle once (lane l those of the pairs
+  // l and, with 16, l + 32) and hands them round; with 32 a lane takes the angles of its own four pairs.
+  constexpr int OWN = LPH == 32 ? 4 : LPH / 8;            // angles a lane takes
+  float freq[OWN];
 #pragma unroll
-  for (int j = 0; j < E / 2; ++j) freq[j] = e0 + 2 * j < rot_dim ? inv_freq[e0 / 2 + j] : 0.f;
+  for (int m = 0; m < OWN; ++m) {
+    const int pair = LPH == 32 ? 4 * lane + m : lane + 32 * m;
+    freq[m] = 2 * pair < rot_dim ? inv_freq[pair] : 0.f;
+  }
   chain_wait();
-  if (item >= (long long)n_tokens * chunks) return;
-  const int t = (int)(item / chunks), h0 = (int)(item % chunks) * hpw, h1 = min(heads, h0 + hpw);
-  const float pos = (float)positions[t];
+  if (item >= n_tokens * chunks) return;                  // (a whole warp: the exchanges below are among the lanes that stay)
+  const int t = item / chunks, h0 = (item % chunks) * hpw, h1 = min(heads, h0 + hpw);
+  // Everything the first round needs from memory is asked for before the angles are taken, so that the loads'
+  // latencies overlap each other and the sines and cosines: the position, the slot, the heads' rows and biases.
+  const int pos_i = positions[t];
+  const int slot = slots ? slots[t] : -1;
+  T* row = qkv + (size_t)t * ld + e0;
+  float x[E], bb[E];
+  bool biased = false;
+  auto fetch = [&](int hb) {
+    const int head = hb + sub;
+#pragma unroll
+    for (int i = 0; i < E; ++i) x[i] = 0.f;
+    biased = false;
+    if (head >= h1) return;
+    LaneRow<T, E>::load(row + (size_t)head * D, x);
+    const float* bias = head < nq ? q_bias : (head < nq + nkv ? k_bias : nullptr);
+    if (bias) {
+      LaneRow<float, E>::load(bias + (size_t)(head < nq ? head : head - nq) * D + e0, bb);
+      biased = true;
+    }
+  };
+  fetch(h0);
+  const float pos = (float)pos_i;
+  float own_cs[OWN], own_sn[OWN];
+#pragma unroll
+  for (int m = 0; m < OWN; ++m) sincosf(pos * freq[m], &own_sn[m], &own_cs[m]);    // (an angle of 0 where nothing is turned)
   float cs[E / 2], sn[E / 2];
 #pragma unroll
   for (int j = 0; j < E / 2; ++j) {
-    cs[j] = 1.f; sn[j] = 0.f;
-    if (e0 + 2 * j < rot_dim) sincosf(pos * freq[j], &sn[j], &cs[j]);
+    if constexpr (LPH == 32) {
+      cs[j] = own_cs[j]; sn[j] = own_sn[j];
+    } else {
+      const int pair = e0 / 2 + j;                        // this lane's j-th pair; its angle is with lane pair % 32
+      float c = __shfl_sync(0xffffffffu, own_cs[0], pair & 31), s = __shfl_sync(0xffffffffu, own_sn[0], pair & 31);
+      if constexpr (OWN == 2) {
+        const float c1 = __shfl_sync(0xffffffffu, own_cs[1], pair & 31), s1 = __shfl_sync(0xffffffffu, own_sn[1], pair & 31);
+        if (pair >= 32) { c = c1; s = s1; }
+      }
+      cs[j] = c; sn[j] = s;
+    }
   }
-  const int slot = slots ? slots[t] : -1;
-  const size_t page = slot >= 0 ? slot / page_size : 0, off = slot >= 0 ? slot % page_size : 0;
-  T* row = qkv + (size_t)t * ld + e0;
-  constexpr int U = 4;                            // heads whose rows are in flight together
-  for (int hb = h0; hb < h1; hb += U) {
-    float xs[U][E];
+  const size_t cache_row = slot >= 0 ? ((size_t)(slot / page_size) * nkv * page_size + slot % page_size) * D + e0 : 0;
+  const size_t head_step = (size_t)page_size * D;        // from one kv head's row of a page to the next head's
+  for (int hb = h0; hb < h1; hb += HW) {
+    if (hb > h0) fetch(hb);
+    const int head = hb + sub;
+    const bool on = head < h1;
+    const bool is_v = on && head >= nq + nkv, is_q = on && head < nq, is_k = on && !is_q && !is_v;
+    if (biased) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (hb + u < h1) LaneRow<T, E>::load(row + (size_t)(hb + u) * D, xs[u]);
+      for (int i = 0; i < E; ++i) x[i] += bb[i];
     }
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int head = hb + u;
-      if (head >= h1) break;
-      float* x = xs[u];
-      T* src = row + (size_t)head * D;
-      if (head >= nq + nkv) {                    // a value head: copied to the cache as it is
-        if (slot >= 0 && v_pages) LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq - nkv)) * page_size + off) * D + e0, x);
-        continue;
-      }
-      const bool is_q = head < nq;
-      const float* bias = is_q ? q_bias : k_bias;
-      if (bias) {
-        float bb[E];
-        LaneRow<float, E>::load(bias + (size_t)(is_q ? head : head - nq) * D + e0, bb);
-#pragma unroll
-        for (int i = 0; i < E; ++i) x[i] += bb[i];
-      }
-      const bool store_kv = !is_q && slot >= 0 && k_pages;
-      if (!is_q && values_are_keys && store_kv && v_pages)
-        LaneRow<T, E>::store(v_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0, x);
-      if (is_q ? q_norm != nullptr : k_norm != nullptr) {
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < E; ++i) ss += x[i] * x[i];
-        const float rs = rsqrtf(warp_sum(ss) / (float)D + eps);
-#pragma unroll
-        for (int i = 0; i < E; ++i) x[i] = x[i] * rs * (is_q ? wq[i] : wk[i]);
-      }
-      T* dst = is_q ? src : (store_kv ? k_pages + ((page * nkv + (head - nq)) * page_size + off) * D + e0 : nullptr);
-      if (!dst) continue;
-#pragma unroll
-      for (int j = 0; j < E / 2; ++j) {
-        if (e0 + 2 * j < rot_dim) {
-          float lo, hi;
-          rotate_pair(x[2 * j], x[2 * j + 1], cs[j], sn[j], lo, hi);
-          x[2 * j] = lo; x[2 * j + 1] = hi;
-        }
-      }
-      LaneRow<T, E>::store(dst, x);
+    if (is_v) {                                  // a value head: copied to the cache as it is
+      if (slot >= 0 && v_pages) LaneRow<T, E>::store(v_pages + cache_row + (size_t)(head - nq - nkv) * head_step, x);
+    } else if (is_k && values_are_keys && slot >= 0 && k_pages && v_pages) {
+      LaneRow<T, E>::store(v_pages + cache_row + (size_t)(head - nq) * head_step, x);
     }
+    // the sum of squares over the lanes of a head; every lane of the warp takes part in the exchange
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < E; ++i) ss += x[i] * x[i];
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (!on || is_v) continue;
+    if (is_q ? q_norm != nullptr : k_norm != nullptr) {
+      const float rs = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+      for (int i = 0; i < E; ++i) x[i] = x[i] * rs * (is_q ? wq[i] : wk[i]);
+    }
+    T* dst = is_q ? row + (size_t)head * D : ((slot >= 0 && k_pages) ? k_pages + cache_row + (size_t)(head - nq) * head_step : nullptr);
+    if (!dst) continue;
+#pragma unroll
+    for (int j = 0; j < E / 2; ++j) {
+      if (e0 + 2 * j < rot_dim) {
+        float lo, hi;
+        rotate_pair(x[2 * j], x[2 * j + 1], cs[j], sn[j], lo, hi);
+        x[2 * j] = lo; x[2 * j + 1] = hi;
+      }
+    }
+    LaneRow<T, E>::store(dst, x);
   }
 }
 
-template <int E>
-void launch_qk_prepare_lanes(cudaStream_t stream, elem_t* qkv, int ld, const float* q_bias, const float* k_bias, const float* q_norm,
-                             const float* k_norm, float eps, const int* positions, const float* inv_freq, int rot_dim,
-                             const int* slots, elem_t* k_pages, elem_t* v_pages, int n_tokens, int nq, int nkv, int page_size,
-                             int values_are_keys) {
+template <int LPH>
+int launch_qk_prepare_lanes(cudaStream_t stream, elem_t* qkv, int ld, const float* q_bias, const float* k_bias, const float* q_norm,
+                            const float* k_norm, float eps, const int* positions, const float* inv_freq, int rot_dim,
+                            const int* slots, elem_t* k_pages, elem_t* v_pages, int n_tokens, int nq, int nkv, int page_size,
+                            int values_are_keys) {
+  constexpr int HW = 32 / LPH;
   const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
-  // heads a warp walks: one while the step is small, up to eight when there are warps enough to fill the GPU many times
-  long long hpw = (long long)n_tokens * heads / 4096;
-  hpw = hpw < 1 ? 1 : (hpw > 8 ? 8 : hpw);
+  // rounds of HW heads a warp walks: one until there are warps enough to fill the GPU four times over, then up to four
+  long long rounds = (long long)n_tokens * heads / (16384LL * HW);
+  rounds = rounds < 1 ? 1 : (rounds > 4 ? 4 : rounds);
+  const int hpw = (int)rounds * HW;
   const long long items = (long long)n_tokens * ((heads + hpw - 1) / hpw);
-  launch_chained(qk_prepare_lanes_kernel<elem_t, E>, dim3((unsigned)((items + kPrepWarps - 1) / kPrepWarps)), dim3(kPrepWarps * 32), 0,
+  if (items > 0x7fffffffLL) return fail(ERB_ERR_UNSUPPORTED, "qk_prepare: %d tokens of %d heads", n_tokens, heads);
+  launch_chained(qk_prepare_lanes_kernel<elem_t, LPH>, dim3((unsigned)((items + kPrepWarps - 1) / kPrepWarps)), dim3(kPrepWarps * 32), 0,
                  stream, qkv, ld, q_bias, k_bias, q_norm, k_norm, eps, positions, inv_freq, rot_dim, slots, k_pages, v_pages, n_tokens,
-                 nq, nkv, page_size, values_are_keys, (int)hpw);
+                 nq, nkv, page_size, values_are_keys, hpw);
+  return ERB_OK;
 }
 
 ERB_EXPORT int erb_qk_prepare(void* qkv, int ld, const float* q_bias, const float* k_bias, const float* q_norm,
@@ -1275,9 +1307,9 @@ ERB_EXPORT int erb_qk_prepare(void* qkv, int ld, const float* q_bias, const floa
 #define ERB_QK(E) launch_qk_prepare_lanes<E>((cudaStream_t)stream, (elem_t*)qkv, ld, q_bias, k_bias, q_norm, k_norm, eps, positions, \
                                              inv_freq, rot_dim, slots, (elem_t*)k_pages, (elem_t*)v_pages, n_tokens, nq, nkv,        \
                                              page_size, values_are_keys)
-    if (head_dim == 64) ERB_QK(2); else if (head_dim == 128) ERB_QK(4); else ERB_QK(8);
+    const int rc = head_dim == 64 ? ERB_QK(8) : (head_dim == 128 ? ERB_QK(16) : ERB_QK(32));
 #undef ERB_QK
-    return check_launch("qk_prepare");
+    return rc ? rc : check_launch("qk_prepare");
   }
   const int heads = nq + nkv + (values_are_keys ? 0 : nkv);
   const long long items = (long long)n_tokens * heads;
