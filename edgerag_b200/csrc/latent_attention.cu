@@ -225,7 +225,7 @@ latent_attention_kernel(const float* __restrict__ q_lat, const T* __restrict__ p
   }
 }
 
-// One block per row: the splits' states merged in split order (a split the row does not reach has l = 0).
+// The splits' states of a row merged in split order (a split the row does not reach has l = 0).
 // The splits' maxima and denominators are fetched by one thread each; every split's weight exp(m_s - m) is
 // taken once and shared.  At most kCombineSplits splits.
 constexpr int kCombineSplits = 128;
@@ -257,7 +257,9 @@ latent_combine_kernel(const float* __restrict__ part, const T* __restrict__ gate
   for (int s = 0; s < n_splits; ++s) l += l_s[s];
   const float f = finish_factor(m, l, sink, h, gate ? Elem<T>::load(gate + (size_t)t * gate_ld + h) : 0.f, gate != nullptr);
   T* o = out + ((size_t)t * H + h) * R;
-  for (int e = threadIdx.x; e < R; e += blockDim.x) {
+  // (gridDim.y blocks share a row, 128 neighbouring columns at a time each: a thread then has one column and its
+  // loads of all splits in flight, instead of a walk over several columns one after the other)
+  for (int e = blockIdx.y * blockDim.x + threadIdx.x; e < R; e += gridDim.y * blockDim.x) {
     float sum = 0.f;
 #pragma unroll 8
     for (int s = 0; s < n_splits; ++s) sum = fmaf(src[s * stride + 2 + e], weight[s], sum);
@@ -635,7 +637,7 @@ ERB_EXPORT int erb_latent_attention(const float* q_lat, const void* pages, const
 #undef ERB_LAT
   int rc = check_launch("latent_attention");
   if (rc || n_splits == 1) return rc;
-  launch_chained(latent_combine_kernel<elem_t>, dim3(n_rows), dim3(128), 0, st, (const float*)part, (const elem_t*)gate, gate_ld,
+  launch_chained(latent_combine_kernel<elem_t>, dim3(n_rows, (R + 127) / 128), dim3(128), 0, st, (const float*)part, (const elem_t*)gate, gate_ld,
                  sink, (elem_t*)out, first_token, H, R, n_splits);
   return check_launch("latent_combine");
 }
@@ -685,7 +687,7 @@ ERB_EXPORT int erb_latent_combine(const float* part, const void* gate, int gate_
                                   int first_token, int n_tokens, int H, int R, int n_splits, void* stream) {
   if (n_tokens <= 0) return ERB_OK;
   if (n_splits < 1 || n_splits > kCombineSplits) return fail(ERB_ERR_ARG, "latent_combine: 1 to %d splits", kCombineSplits);
-  launch_chained(latent_combine_kernel<elem_t>, dim3(n_tokens * H), dim3(128), 0, (cudaStream_t)stream, part, (const elem_t*)gate,
+  launch_chained(latent_combine_kernel<elem_t>, dim3(n_tokens * H, (R + 127) / 128), dim3(128), 0, (cudaStream_t)stream, part, (const elem_t*)gate,
                  gate_ld, sink, (elem_t*)out, first_token, H, R, n_splits);
   return check_launch("latent_combine");
 }
