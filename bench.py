@@ -687,10 +687,22 @@ def run_vokusun(args, measure, n_runs: int, block: int, clocks, peak_source: str
         "latent_attention_decode_b8_ctx8192": microbench.latent_attention(ns(batch=8, context=8192, tokens=0, past=0, cold=True, **lat)),
         "latent_attention_prefill_2048": microbench.latent_attention(ns(batch=1, context=0, tokens=2048, past=0, cold=False, **lat)),
     }
+    # in a process of its own, whose launches are not chained from the first one on: only then is a kernel's time under
+    # the tracer its own (a chained kernel is resident, waiting, while the kernel before it still runs)
+    import subprocess
+    import tempfile
+
     steps = {}
     for name, cfg in (("vokusun", vokusun_config(size, 3)), ("llama", llama_config(size, 3, 8))):
-        steps[name] = microbench.step_kernels(types.SimpleNamespace(config=cfg, vocab=size["vocab"], layers=3, heads=32, kv_heads=8, batch=args.batch, context=2048,
-                                                                    tokens=2048, iters=4, rows=16))
+        with tempfile.NamedTemporaryFile("w", suffix=".json") as f:
+            json.dump(cfg, f)
+            f.flush()
+            done = subprocess.run([sys.executable, "-m", "edgerag_b200.ops.microbench", "step-kernels", "--config-json", f.name,
+                                   "--batch", str(args.batch), "--context", "2048", "--tokens", "2048", "--iters", "4", "--rows", "16"],
+                                  cwd=str(ROOT), env=dict(os.environ, EDGERAG_B200_NO_CHAIN="1"), capture_output=True, text=True)
+        if done.returncode != 0:
+            raise RuntimeError(f"step-kernels of {name} failed: {done.stderr[-400:]}")
+        steps[name] = json.loads(done.stdout.strip().splitlines()[-1])
     return {"metric": "design_compare", "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "dtype": "bf16",
             "data": "synthetic", "impl": "ours", "higher_is_better": True,
             "config": {"designs": ["Vokusun", "Llama decoder"], "prefill_tokens": 2048, "decode_context": 2048,

@@ -218,9 +218,12 @@ def step_kernels(a) -> dict:
            "num_attention_heads": a.heads, "num_key_value_heads": a.kv_heads, "head_dim": 64, "intermediate_size": 8192,
            "vocab_size": 49155, "rope_theta": 273768.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
            "hidden_act": "silu", "max_position_embeddings": 8192, "pad_token_id": 0}
+    if getattr(a, "config_json", None):       # any model: a config.json (its vocabulary size is searched under the usual keys)
+        with open(a.config_json) as f:
+            cfg = json.load(f)
     cfg = getattr(a, "config", None) or cfg
-    vocab = getattr(a, "vocab", None) or 49155
-    rows_shown = getattr(a, "rows", 12)
+    vocab = getattr(a, "vocab", None) or cfg.get("vocab_size") or cfg.get("vocab") or 49155
+    rows_shown = getattr(a, "rows", None) or 12
     eng = Engine.from_config(cfg, 0, 0.02, EngineOptions(
         dtype="bfloat16", block_size=16, num_blocks=a.batch * (a.context // 16 + 2) + a.tokens // 16 + 64,
         max_batch_size=a.batch + 2, chunk_size=a.tokens, max_step_tokens=a.tokens + a.batch, max_model_len=a.context + 8,
@@ -442,6 +445,8 @@ def main(argv=None) -> int:
     k.add_argument("--tokens", type=int, default=2048)
     k.add_argument("--heads", type=int, default=32)
     k.add_argument("--kv-heads", type=int, default=32)
+    k.add_argument("--config-json", default=None, help="a config.json of any registered architecture instead of the SmolVLM-2.2B sizes")
+    k.add_argument("--rows", type=int, default=12, help="kernels listed per table")
     t = sub.add_parser("step-timeline", parents=[common])
     t.add_argument("--layers", type=int, default=4)
     t.add_argument("--batch", type=int, default=8)
