@@ -681,7 +681,8 @@ def run_vokusun(args, measure, n_runs: int, block: int, clocks, peak_source: str
         "window_attention_prefill_8192": pre(8192, window=win, keep_first=keep),
         "llama_attention_prefill_8192": pre(8192),
         # a token of a windowed layer reads its window and the kept keys: the same bytes as a context of that length
-        "window_attention_decode_b64_ctx8192": dec(context=8192, kernel="bulk", window=win, keep_first=keep),
+        "window_attention_decode_b64_ctx8192_gqa": dec(context=8192, kernel="gqa", window=win, keep_first=keep),
+        "window_attention_decode_b64_ctx8192_bulk": dec(context=8192, kernel="bulk", window=win, keep_first=keep),
         "llama_attention_decode_b64_ctx1024_bulk": dec(context=1024, kernel="bulk"),
         "llama_attention_decode_b64_ctx1024_gqa": dec(context=1024, kernel="gqa"),
         "latent_attention_decode_b8_ctx8192": microbench.latent_attention(ns(batch=8, context=8192, tokens=0, past=0, cold=True, **lat)),

@@ -560,7 +560,7 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             float* __restrict__ part_acc, float* __restrict__ part_ml, int max_splits, int nq,
                             int nkv, int page_size, int split_keys, float scale_log2, int hg,
                             __nv_bfloat16* __restrict__ out, int out_row_stride, int* __restrict__ status,
-                            int* __restrict__ counters) {
+                            int* __restrict__ counters, int window, int keep_first) {
   constexpr int D = 64;
   const int R = nq / nkv;
   extern __shared__ uint8_t smem_raw[];
@@ -583,11 +583,22 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int stage_keys = kGqaStageRows / hg;               // keys of each head per stage
   const int t = token_of_seq[seq];
   const int pos = positions[t];
-  const int begin = split * split_keys;
-  const int end = min(pos + 1, begin + split_keys);
+  // A window: as in the kernel above (whole pages are copied, so the first split starts at the page of the window's
+  // first key, the keys before it are masked, and the first split walks the kept keys first).
+  const int k_lo = window > 0 ? max(pos - window + 1, 0) : 0;
+  const int first_split = k_lo / split_keys;
+  const int k_first = (k_lo / page_size) * page_size;
+  const int begin = max((first_split + split) * split_keys, k_first);
+  const int end = min(pos + 1, (first_split + split + 1) * split_keys);
   if (begin >= end) return;
   const int* bt = block_tables + (size_t)seq * max_pages;
-  const int n_tiles = (end - begin + stage_keys - 1) / stage_keys;
+  const int kept = (window > 0 && split == 0) ? min(keep_first, k_first) : 0;
+  const int kept_tiles = (kept + stage_keys - 1) / stage_keys;
+  const int n_tiles = kept_tiles + (end - begin + stage_keys - 1) / stage_keys;
+  auto tile_begin = [&](int tile) { return tile < kept_tiles ? tile * stage_keys : begin + (tile - kept_tiles) * stage_keys; };
+  auto tile_end = [&](int tile) {
+    return tile < kept_tiles ? min(kept, (tile + 1) * stage_keys) : min(end, begin + (tile - kept_tiles + 1) * stage_keys);
+  };
 
   if (tid == 0) {
 #pragma unroll
@@ -601,6 +612,8 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const int first_page = begin / page_size;
   const int n_pages = (end - 1) / page_size - first_page + 1;
   for (int i = tid; i < n_pages; i += kGqaThreads) s_pages[i] = bt[first_page + i];
+  int* s_kept = s_pages + split_keys / page_size + 2;     // the pages of the kept keys
+  for (int i = tid; i * page_size < kept; i += kGqaThreads) s_kept[i] = bt[i];
   __syncthreads();
   // A wait that gives up when its own limit runs out or when another thread of the block has given up.
   auto wait_for = [&](uint32_t bar, uint32_t parity) {
@@ -623,12 +636,13 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   const uint32_t page_bytes = (uint32_t)(hg_here * page_size) * 128u;    // what one page brings
   auto issue = [&](int tile) {   // one lane of the copy warp: whole pages, hg_here * page_size rows per copy
     const int s = tile % kGqaStages;
-    const int kb = begin + tile * stage_keys, ke = min(end, kb + stage_keys);
+    const int kb = tile_begin(tile), ke = tile_end(tile);
+    const int* pages_of_tile = tile < kept_tiles ? s_kept : s_pages - first_page;
     const uint32_t bar = sBar + 8 * s;
     const int n_pg = (ke - kb + page_size - 1) / page_size;
     mbar_expect(bar, (uint32_t)n_pg * page_bytes * 2);
     for (int j = 0; j < n_pg; ++j) {
-      const int page = s_pages[kb / page_size + j - first_page];
+      const int page = pages_of_tile[kb / page_size + j];
       const int row = (page * nkv + kvh0) * page_size;
       const uint32_t dst = (uint32_t)s * kGqaStageBytes + (uint32_t)j * page_slot;
       tma_load_rows(sK + dst, mk, row, bar);
@@ -643,7 +657,7 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
       const int old_end = (pos / page_size) * page_size;
       bool waited = false;
       for (int tile = 0; tile < n_tiles; ++tile) {
-        if (!waited && min(end, begin + (tile + 1) * stage_keys) > old_end) { chain_wait(); waited = true; }
+        if (!waited && tile_end(tile) > old_end) { chain_wait(); waited = true; }
         if (tile >= kGqaStages && !wait_for(sEmpty + 8 * (tile % kGqaStages), ((tile / kGqaStages) - 1) & 1)) break;
         issue(tile);
       }
@@ -684,7 +698,8 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int s = tile % kGqaStages;
     if (warp == kDecWarps) break;                           // the copy warp has nothing to multiply
     if (ok && !wait_for(sBar + 8 * s, (tile / kGqaStages) & 1)) ok = false;
-    const int n_here = min(end - (begin + tile * stage_keys), stage_keys);
+    const int n_here = tile_end(tile) - tile_begin(tile);
+    const int key_abs0 = tile_begin(tile);
     if (ok && serves && key0 < n_here) {
       const uint32_t k_st = sK + (uint32_t)s * kGqaStageBytes, v_st = sV + (uint32_t)s * kGqaStageBytes;
       // Rows past the last key may hold anything (unwritten slots, an earlier tile): their scores are
@@ -717,18 +732,21 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           const int key = key0 + 8 * b + 2 * j + i;
-          sc[b][i] = key < n_here ? sc[b][i] * scale_log2 : -INFINITY;
+          // (keys past the split's end, and keys of the window's first page that lie before the window and are not kept)
+          const bool seen = key < n_here && !(key_abs0 + key < k_lo && key_abs0 + key >= keep_first);
+          sc[b][i] = seen ? sc[b][i] * scale_log2 : -INFINITY;
           m_new = fmaxf(m_new, sc[b][i]);
         }
       m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 1));
       m_new = fmaxf(m_new, __shfl_xor_sync(0xffffffffu, m_new, 2));
-      // key0 < n_here: the row has at least one real key, so m_new is finite
-      const float a = exp2f(m_run - m_new);
+      // (all of the row's keys may be hidden so far: exponentials are then taken against 0 and are 0)
+      const float m_ref = m_new == -INFINITY ? 0.f : m_new;
+      const float a = exp2f(m_run - m_ref);
       float p[2][2], sum = 0.f;
 #pragma unroll
       for (int b = 0; b < 2; ++b)
 #pragma unroll
-        for (int i = 0; i < 2; ++i) { p[b][i] = exp2f(sc[b][i] - m_new); sum += p[b][i]; }
+        for (int i = 0; i < 2; ++i) { p[b][i] = exp2f(sc[b][i] - m_ref); sum += p[b][i]; }
       l_run = l_run * a + sum;
       m_run = m_new;
       const uint32_t pa0 = pack_bf16(p[0][0], p[0][1]), pa2 = pack_bf16(p[1][0], p[1][1]);
@@ -784,7 +802,7 @@ attention_decode_gqa_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   }
   if (max_splits > 1 && counters)
     merge_splits_if_last<D>(counters + (size_t)seq * gridDim.y + blockIdx.y, part_acc, part_ml,
-                            (size_t)seq * nq + (size_t)kvh0 * R, hg_here * R, min(pos / split_keys + 1, max_splits), max_splits,
+                            (size_t)seq * nq + (size_t)kvh0 * R, hg_here * R, min(pos / split_keys - first_split + 1, max_splits), max_splits,
                             out + (size_t)t * out_row_stride + (size_t)kvh0 * R * D);
 }
 
@@ -806,8 +824,10 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
                                         const int* token_of_seq, const int* positions, void* out, int out_row_stride,
                                         float* part_acc, float* part_ml, int max_splits, int n_seqs, int nq, int nkv,
                                         int head_dim, int page_size, int split_keys, float scale, int* status,
-                                        int* counters, void* stream) {
+                                        int* counters, int window, int keep_first, void* stream) {
   if (n_seqs <= 0) return ERB_OK;
+  window = window > 0 ? window : 0;
+  keep_first = window > 0 && keep_first > 0 ? keep_first : 0;
   if (!erb_attention_decode_gqa_supported(nq, nkv, head_dim, page_size, split_keys))
     return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: %d/%d heads of %d, pages of %d, splits of %d", nq, nkv,
                 head_dim, page_size, split_keys);
@@ -830,7 +850,7 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
     return rc;
   const int r = nq / nkv;
   const size_t smem = 1024 + 2 * kGqaStages * kGqaStageBytes + 64 + (size_t)kDecWarps * r * (64 + 2) * sizeof(float) + 128 +
-                      (size_t)(split_keys / page_size + 2) * sizeof(int);
+                      (size_t)(split_keys / page_size + 2 + (window > 0 ? keep_first / page_size + 1 : 0)) * sizeof(int);
   if (smem > 200 * 1024) return fail(ERB_ERR_UNSUPPORTED, "attention_decode_gqa: split of %d keys in pages of %d", split_keys, page_size);
   static size_t configured = 0;
   if (smem > configured) {
@@ -843,11 +863,11 @@ ERB_EXPORT int erb_attention_decode_gqa(const void* q, int q_row_stride, const v
   launch_chained(attention_decode_gqa_kernel, dim3(dim3(max_splits, (nkv + hg - 1) / hg, n_seqs)), dim3(kGqaThreads), smem, s,
                  mk, mv, mkl, mvl, (const __nv_bfloat16*)q, q_row_stride, block_tables, max_pages, token_of_seq, positions,
                  part_acc, part_ml, max_splits, nq, nkv, page_size, split_keys, scale_log2, hg, (__nv_bfloat16*)out, out_row_stride,
-                 status, counters);
+                 status, counters, window, keep_first);
   // a single split wrote the result itself; with counters the block that finishes last merges the splits
   if ((rc = check_launch("attention_decode_gqa")) || max_splits == 1 || counters) return rc;
   launch_chained(attention_decode_bulk_combine_kernel, dim3(dim3(nq, n_seqs)), dim3(64), 0, s, part_acc, part_ml, token_of_seq, positions,
-      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys, 0);
+      (__nv_bfloat16*)out, out_row_stride, max_splits, nq, head_dim, split_keys, window);
   return check_launch("attention_decode_bulk_combine");
 }
 

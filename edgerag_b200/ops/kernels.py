@@ -65,7 +65,7 @@ _SIGNATURES = {
                                   c_int, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "erb_attention_decode_gqa": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                 c_float, c_void_p, c_void_p, c_void_p],
+                                 c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "erb_glu_bounded": [c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
     "erb_add_layernorm": [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_float,
                           c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -1158,8 +1158,8 @@ def attention_decode_bulk(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch
 def decode_gqa_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_heads: int, n_kv_heads: int,
                          page_size: int, split_keys: int, max_splits: int = 1) -> bool:
     """Shapes the tensor-core decode kernel for grouped query heads takes: bfloat16, head size 64,
-    2 to 8 query heads per kv head, pages of a multiple of 8 tokens, no window."""
-    if dtype != torch.bfloat16 or window > 0 or max_splits > 64 or head_dim != 64 or n_q_heads == n_kv_heads:
+    2 to 8 query heads per kv head, pages of a multiple of 8 tokens, with or without a window."""
+    if dtype != torch.bfloat16 or max_splits > 64 or head_dim != 64 or n_q_heads == n_kv_heads:
         return False        # (answered here so that other models need not build the tensor-core library)
     return bool(native.load("attention_tc", None).erb_attention_decode_gqa_supported(
         n_q_heads, n_kv_heads, head_dim, page_size, int(split_keys)))
@@ -1168,8 +1168,9 @@ def decode_gqa_supported(dtype: torch.dtype, head_dim: int, window: int, n_q_hea
 def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_tables: torch.Tensor,
                          token_of_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor, n_q_heads: int,
                          scale: float, part_acc: torch.Tensor, part_ml: torch.Tensor, max_splits: int,
-                         status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS) -> None:
-    """``attention_decode`` for several query heads per kv head on tensor cores: the query heads of a
+                         status: torch.Tensor, split_keys: int = DECODE_SPLIT_KEYS, window: int = 0, keep_first: int = 0) -> None:
+    """``attention_decode`` for several query heads per kv head on tensor cores (``window`` and ``keep_first`` as in
+    ``attention_decode_bulk``): the query heads of a
     kv head are the rows of one matrix tile, pages arrive by TMA tensor copies."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pages, "k_pages", torch.bfloat16)
     _need(v_pages, "v_pages", torch.bfloat16); _need(block_tables, "block_tables", torch.int32)
@@ -1187,7 +1188,7 @@ def attention_decode_gqa(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
           v_pages.data_ptr(), n_pages, block_tables.data_ptr(), block_tables.shape[1], token_of_seq.data_ptr(),
           positions.data_ptr(), out.data_ptr(), out.stride(0), part_acc.data_ptr(), part_ml.data_ptr(), max_splits,
           n_seqs, n_q_heads, nkv, d, page_size, int(split_keys), float(scale), status.data_ptr(),
-          split_counters(q.device, n_seqs * nkv).data_ptr(), _stream())
+          split_counters(q.device, n_seqs * nkv).data_ptr(), int(window), int(keep_first), _stream())
 
 
 #: query rows of one (sequence, head) that a block of the tensor-core prefill kernel takes

@@ -112,7 +112,7 @@ def decode_attention(a) -> dict:
                                                     granule * a.page)
         a.head_group = a.head_group or heads
     splits = (a.context - 1) // a.split + 1
-    if window > 0 and a.kernel != "gqa":
+    if window > 0:
         splits = min(splits, window // a.split + 2)
     acc_n, ml_n = kernels.decode_scratch_floats(a.batch, a.heads, a.head_dim, splits)
     acc, ml = torch.empty(acc_n, device="cuda"), torch.empty(ml_n, device="cuda")
@@ -120,7 +120,7 @@ def decode_attention(a) -> dict:
     scale = a.head_dim ** -0.5
     if a.kernel == "gqa":
         fn = lambda: kernels.attention_decode_gqa(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
-                                                  status, split_keys=a.split)
+                                                  status, split_keys=a.split, window=window, keep_first=keep)
     elif a.kernel == "bulk":
         fn = lambda: kernels.attention_decode_bulk(q, *cache(), tok, pos, out, a.heads, scale, acc, ml, splits,  # noqa: E731
                                                    status, split_keys=a.split, head_group=a.head_group, window=window, keep_first=keep)

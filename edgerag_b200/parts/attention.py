@@ -127,7 +127,7 @@ class Attention(Mixer):
             elif self.window > 0:       # a token reads its window and the kept keys, however long its context is
                 reach = min(ctx.max_keys_bound(), -(-(self.window + self.keep_first) // ctx.page_size) * ctx.page_size)
                 split, heads_per_block = kernels.choose_decode_plan(nd, self.n_kv, reach, ctx.page_size, d,
-                                                                    self.dtype != torch.bfloat16, reach)
+                                                                    grouped or self.dtype != torch.bfloat16, reach)
             else:
                 split, heads_per_block = kernels.choose_decode_plan(nd, self.n_kv, ctx.max_keys_bound(), ctx.page_size, d,
                                                                     grouped or self.dtype != torch.bfloat16, ctx.keys_granule())
@@ -138,7 +138,7 @@ class Attention(Mixer):
             if kernels.decode_gqa_supported(self.dtype, d, self.window, self.n_q, self.n_kv, ctx.page_size, split, max_splits):
                 kernels.attention_decode_gqa(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                              out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,
-                                             split_keys=split)
+                                             split_keys=split, window=self.window, keep_first=self.keep_first)
             elif kernels.decode_bulk_supported(self.dtype, d, self.window, self.n_q, self.n_kv, max_splits):
                 kernels.attention_decode_bulk(qkv[:nd], k_pages, v_pages, tables, ctx.token_of_seq[:nd], ctx.positions,
                                               out[:nd], self.n_q, self.scale, part_acc, part_ml, max_splits, ctx.status,

@@ -410,7 +410,7 @@ def _paged(rows, page_size, dtype, shuffle_seed=0):
 
 WINDOW_CASES = [  # (heads, kv heads, head size, page, window, kept)
     (4, 2, 32, 16, 24, 5), (6, 1, 48, 8, 17, 0), (2, 2, 64, 16, 64, 16), (8, 2, 128, 32, 40, 33), (3, 3, 16, 16, 9, 20),
-    (4, 2, 24, 16, 30, 2), (6, 2, 64, 8, 100, 12), (8, 1, 32, 16, 33, 40),
+    (4, 2, 24, 16, 30, 2), (6, 2, 64, 8, 100, 12), (8, 1, 32, 16, 33, 40), (8, 2, 64, 16, 40, 21), (4, 2, 64, 32, 200, 70),
 ]
 
 
@@ -473,6 +473,15 @@ def test_window_attention_with_one_key_made_dominant(case, dtype):
                            splits, window=window, split_keys=split, keep_first=keep)
         err = (out1.double().cpu().reshape(n, H, d) - want).abs().amax((1, 2))
         assert err.max() < tol, f"single tokens, splits of {split}: query {int(err.argmax())} {where[int(err.argmax())]}: {err.max():.2e}"
+        if k.decode_gqa_supported(tdt, d, window, H, G, page, split, splits):
+            # grouped query heads of 64 on tensor cores
+            out4 = torch.full_like(qd, float("nan"))
+            status = torch.zeros(1, dtype=torch.int32, device="cuda")
+            k.attention_decode_gqa(qd, kp, vp, tables1, tok, pos, out4, H, 0.5, torch.empty(acc, device="cuda"),
+                                   torch.empty(ml, device="cuda"), splits, status, split_keys=split, window=window, keep_first=keep)
+            assert int(status.item()) == 0
+            err = (out4.double().cpu().reshape(n, H, d) - want).abs().amax((1, 2))
+            assert err.max() < tol, f"grouped heads, splits of {split}: query {int(err.argmax())} {where[int(err.argmax())]}: {err.max():.2e}"
         if k.decode_bulk_supported(tdt, d, window, H, G, splits):
             # the kernel that streams pages with bulk copies: one kv head per block, and as many as it likes to group
             for group in (1, 0):
